@@ -1,0 +1,98 @@
+// Bit-level pieces of the EXL3 trellis decoder that are plain integer arithmetic:
+// which words of a packed tile a fragment lane needs, how the eight 16-bit
+// codeword windows are cut out of them, and the integer half of the three
+// codebooks.  Everything here compiles for host and device, so the lane
+// arithmetic is exercised on the CPU (tests/host_emul) against the oracle
+// before any kernel runs.
+//
+// Tile format (reference: ponyexl3/ref/trellis.py:105-141): a 16x16 tile is
+// 256 codewords of K fresh bits each, stored as 8K little-endian uint32 words
+// read MSB-first; codeword c is the 16-bit window of that circular 256K-bit
+// stream ending at bit (c+1)K.  Codeword index 8t+j belongs to fragment lane t
+// (reference: ponyexl3/ref/perm.py:8-26), so lane t needs stream bits
+// [8tK + K - 16, 8tK + 8K): 7K+16 bits, at most three words.
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define EXL3_HD __host__ __device__ __forceinline__
+#else
+#define EXL3_HD inline
+#endif
+
+namespace exl3 {
+
+enum : int { CB_3INST = 0, CB_MCG = 1, CB_MUL1 = 2 };
+
+// High 32 bits of ((hi:lo) << s), 0 <= s < 32.
+EXL3_HD uint32_t funnel_l(uint32_t lo, uint32_t hi, uint32_t s)
+{
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_l(lo, hi, s);
+#else
+    return s == 0 ? hi : ((hi << s) | (lo >> (32 - s)));
+#endif
+}
+
+// Which words of its tile a lane reads, and how far its window starts inside
+// the first one.  Constant for a lane over the whole kernel.
+template <int K> struct LaneWords {
+    static constexpr int kWords = 8 * K;          // uint32 words per tile
+    static constexpr bool kThree = (K >= 5);      // third word ever needed
+    int i0, i1, i2;                               // word indices inside the tile
+    uint32_t sh;                                  // bit offset of the window in word i0
+
+    EXL3_HD void init(int lane)
+    {
+        int p0 = 8 * lane * K + K - 16;           // first stream bit the lane needs
+        if (p0 < 0) p0 += 256 * K;                // tail-biting: wraps to the tile's end
+        i0 = p0 >> 5;
+        sh = (uint32_t)(p0 & 31);
+        i1 = i0 + 1; if (i1 >= kWords) i1 -= kWords;
+        i2 = i1 + 1; if (i2 >= kWords) i2 -= kWords;
+    }
+};
+
+// The eight codewords of a lane from its (up to) three words a, b, c, taken in
+// stream order.  Output values are zero-extended 16-bit windows.
+template <int K> EXL3_HD void lane_codewords(uint32_t a, uint32_t b, uint32_t c, uint32_t sh,
+                                             uint32_t (&cw)[8])
+{
+    // Left-align the lane's 7K+16 bits: n[0] bit 31 is stream bit p0.
+    uint32_t n[3];
+    n[0] = funnel_l(b, a, sh);
+    n[1] = LaneWords<K>::kThree ? funnel_l(c, b, sh) : (b << sh);
+    n[2] = LaneWords<K>::kThree ? (c << sh) : 0u;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int off = j * K;                    // window j = bits [off, off+16) of n
+        const int q = off >> 5, r = off & 31;
+        if (r + 16 <= 32) cw[j] = (n[q] >> (16 - r)) & 0xFFFFu;
+        else cw[j] = funnel_l(n[q + 1 > 2 ? 2 : q + 1], n[q], (uint32_t)r) >> 16;
+    }
+}
+
+// Integer part of the codebooks (reference: ponyexl3/ref/codebook.py:66-91).
+// 3INST and MCG: a 32-bit word whose two fp16 halves sum to the weight.
+// MUL1: the fp16 bit pattern 0x6400 + (sum of the product's bytes), to be sent
+// through one fused multiply-add.
+template <int CB> EXL3_HD uint32_t codebook_word(uint32_t cw)
+{
+    if (CB == CB_MUL1) {
+        uint32_t x = cw * 0x83DCD12Du;
+#if defined(__CUDA_ARCH__)
+        return __dp4a(x, 0x01010101u, 0x6400u);
+#else
+        return 0x6400u + (x & 0xFFu) + ((x >> 8) & 0xFFu) + ((x >> 16) & 0xFFu) + (x >> 24);
+#endif
+    }
+    uint32_t x = (CB == CB_3INST) ? cw * 89226354u + 64248484u : cw * 0xCBAC1FEDu;
+    return (x & 0x8FFF8FFFu) ^ 0x3B603B60u;
+}
+
+// Tile position (row = input-feature offset, col = output-feature offset) of
+// codeword j of lane t (reference: ponyexl3/ref/perm.py:8-26).
+EXL3_HD int frag_row(int t, int j) { return (t & 3) * 2 + (j & 1) + ((j & 2) ? 8 : 0); }
+EXL3_HD int frag_col(int t, int j) { return (t >> 2) + ((j & 4) ? 8 : 0); }
+
+}  // namespace exl3
