@@ -1,0 +1,122 @@
+/*
+ * exl3_b200 — C ABI of the B200 (sm_100a) EXL3 fused dequant-matmul path.
+ *
+ * Drop-in boundary for the EXL3 linear-module path of PonyExl3: a host program
+ * (PyTorch via ctypes, or any FFI) owns every buffer and passes plain device
+ * pointers, sizes and a CUDA stream; nothing is allocated or freed in here and
+ * there is no CPU fallback.  Every entry point validates its arguments on the
+ * host before launching and returns 0 or a negative EXL3_E* code; kernels are
+ * enqueued on `stream` and the call returns without synchronising.
+ *
+ * Data formats are the reference's (paths are inside the reference project):
+ *   trellis  (in/16, out/16, 16*K) uint16, C order   ponyexl3/ref/layer.py:12-44
+ *   suh/svh  (in,) / (out,) fp16 multipliers or NULL  ponyexl3/ref/signs.py:22-27
+ *   bias     (out,) fp16 or NULL
+ *   K        1..8 bits per weight; cb 0 = 3INST, 1 = MCG, 2 = MUL1
+ *                                                      ponyexl3/ref/codebook.py:9-12,94-99
+ * All fp16 buffers are passed as uint16_t* (bit patterns).
+ */
+#ifndef EXL3_B200_H
+#define EXL3_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EXL3_B200_VERSION 100
+
+#if defined(__GNUC__)
+#define EXL3_API __attribute__((visibility("default")))
+#else
+#define EXL3_API
+#endif
+
+/* error codes */
+#define EXL3_OK 0
+#define EXL3_E_NULL (-1)        /* a required pointer is NULL */
+#define EXL3_E_K (-2)           /* K outside 1..8 */
+#define EXL3_E_CODEBOOK (-3)    /* cb outside 0..2 */
+#define EXL3_E_SHAPE (-4)       /* a dimension is zero, negative or not a multiple of 16 / 128 */
+#define EXL3_E_ROWS (-5)        /* row count outside what the entry point supports */
+#define EXL3_E_ALIGN (-6)       /* a pointer or stride is not aligned as required */
+#define EXL3_E_WORKSPACE (-7)   /* workspace missing or too small */
+#define EXL3_E_DTYPE (-8)       /* unknown activation dtype */
+#define EXL3_E_CUDA (-9)        /* a CUDA runtime call failed (see exl3_last_cuda_error) */
+#define EXL3_E_RANGE (-10)      /* an index or slice is out of range */
+#define EXL3_E_UNSUPPORTED (-11)
+
+/* activation dtypes */
+#define EXL3_DT_F16 0
+#define EXL3_DT_BF16 1
+#define EXL3_DT_F32 2
+
+/* flags */
+#define EXL3_FLAG_PDL 1u        /* launch with programmatic stream serialisation so the next
+                                   kernel's weight prefetch overlaps this kernel's tail */
+
+typedef void* exl3_stream_t;    /* cudaStream_t */
+
+EXL3_API int exl3_version(void);
+EXL3_API const char* exl3_error_string(int code);
+/* Text of the last CUDA runtime error seen by this thread inside the library. */
+EXL3_API const char* exl3_last_cuda_error(void);
+
+/* ---- codec pieces (tests, debugging; reference: ponyexl3/ref) ------------------------- */
+
+/* Packed tiles -> 256 uint16 codewords per tile.
+ * Replaces unpack_trellis, ponyexl3/ref/trellis.py:205-214 (Metal twin
+ * exl3_unpack_trellis_k{K}_v2, ponyexl3/mlx/metal_kernels.py:59-87). */
+EXL3_API int exl3_unpack(const uint16_t* trellis, int64_t n_tiles, int k, uint16_t* codewords,
+                exl3_stream_t stream);
+
+/* Packed trellis -> inner weight matrix W (16*t_in rows, ld columns) fp16, out-tiles
+ * [tn0, tn0+tn_count).  Bit-exact with decode_packed_trellis, ponyexl3/ref/decode.py:32-81 /
+ * reconstruct_inner, ponyexl3/ref/reconstruct.py:13-23.  A test and debugging aid: the
+ * matmul entry points never materialise W. */
+EXL3_API int exl3_decode(const uint16_t* trellis, int64_t t_in, int64_t t_out, int k, int cb, int64_t tn0,
+                int64_t tn_count, uint16_t* w, int64_t ld, exl3_stream_t stream);
+
+/* All 65,536 codewords of a codebook -> fp16.  decode_3inst, ponyexl3/ref/codebook.py:66-91. */
+EXL3_API int exl3_codebook_table(int cb, uint16_t* table65536, exl3_stream_t stream);
+
+/* out = fp16( ((x * pre) @ H128 / sqrt(128)) * post ) per 128-wide block of the last
+ * dimension; pre/post fp16 vectors of length n or NULL; x rows are x_row_stride elements
+ * apart.  Replaces had_r_128, ponyexl3/ref/hadamard.py:50-80 (runtime twin prepare_xh /
+ * finish_y, ponyexl3/mlx/layer_state.py:121-141). */
+EXL3_API int exl3_hadamard128(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
+                     const uint16_t* pre, const uint16_t* post, uint16_t* out,
+                     exl3_stream_t stream);
+
+/* ---- workspace ------------------------------------------------------------------------- */
+
+/* Bytes of scratch the matmul entry points need for activations of up to `max_rows` rows
+ * (counting every member of a sibling group and every MoE slot) and `max_in` input
+ * features.  The caller allocates it (256-byte aligned) and calls exl3_workspace_init once
+ * before first use; calls that share a workspace must be ordered on one stream. */
+EXL3_API size_t exl3_workspace_bytes(int64_t max_rows, int64_t max_in);
+EXL3_API int exl3_workspace_init(void* workspace, size_t bytes, exl3_stream_t stream);
+/* Device-side status word of the workspace (0 = no kernel reported a bounded wait giving
+ * up); copies it to *status_out after synchronising the stream. */
+EXL3_API int exl3_workspace_status(const void* workspace, int* status_out, exl3_stream_t stream);
+
+/* ---- the linear forward ------------------------------------------------------------------ */
+
+/* y[rows, out] = fp16( had( fp16( fp16(had(x * suh)) @ W ) ) * svh ) + bias, rows 1..16:
+ * the decode-time GEMV (rows = 1) and the small-batch verify GEMV (2..16).  The packed
+ * trellis is streamed once, decoded in registers, accumulated in fp32.
+ * Replaces EXL3Linear.__call__ rows<=16, ponyexl3/mlx/exl3_linear.py:98-136, i.e.
+ * prepare_xh + inner_gemv_mlx / inner_gemm_mlx (ponyexl3/mlx/gemv_metal.py:1340-1478) +
+ * finish_y; contract linear_forward_reconstruct, ponyexl3/ref/forward.py:14-49.
+ * x rows are x_row_stride elements apart; y rows are y_row_stride elements apart. */
+EXL3_API int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const uint16_t* trellis,
+              int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
+              const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
+              size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXL3_B200_H */

@@ -1,0 +1,216 @@
+// extern "C" surface of libexl3b200.so: argument validation on the host, then the
+// kernel launchers.  No allocation, no global mutable state beyond per-device
+// caches of immutable facts (SM count, function attributes).
+#include <string.h>
+
+#include "exl3_internal.h"
+
+namespace exl3 {
+
+static thread_local char g_cuda_err[256] = "";
+
+int note_cuda(cudaError_t e)
+{
+    if (e == cudaSuccess) return EXL3_OK;
+    strncpy(g_cuda_err, cudaGetErrorString(e), sizeof(g_cuda_err) - 1);
+    g_cuda_err[sizeof(g_cuda_err) - 1] = 0;
+    return EXL3_E_CUDA;
+}
+
+int check_launch() { return note_cuda(cudaGetLastError()); }
+
+int device_sm_count()
+{
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+void gemv_set_tuning(int ctas_per_sm, int smem_budget_bytes);
+
+static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+}  // namespace exl3
+
+using namespace exl3;
+
+extern "C" {
+
+int exl3_version(void) { return EXL3_B200_VERSION; }
+
+const char* exl3_error_string(int code)
+{
+    switch (code) {
+        case EXL3_OK: return "ok";
+        case EXL3_E_NULL: return "a required pointer is NULL";
+        case EXL3_E_K: return "K must be in [1, 8]";
+        case EXL3_E_CODEBOOK: return "unknown codebook mode (0 = 3INST, 1 = MCG, 2 = MUL1)";
+        case EXL3_E_SHAPE: return "bad shape: features must be positive multiples of 128 (tiles of 16)";
+        case EXL3_E_ROWS: return "row count outside the supported range of this entry point";
+        case EXL3_E_ALIGN: return "pointer or stride not aligned as required";
+        case EXL3_E_WORKSPACE: return "workspace missing or too small";
+        case EXL3_E_DTYPE: return "unknown activation dtype";
+        case EXL3_E_CUDA: return "CUDA runtime error";
+        case EXL3_E_RANGE: return "index or slice out of range";
+        case EXL3_E_UNSUPPORTED: return "configuration not supported";
+        default: return "unknown error code";
+    }
+}
+
+const char* exl3_last_cuda_error(void) { return g_cuda_err; }
+
+int exl3_unpack(const uint16_t* trellis, int64_t n_tiles, int k, uint16_t* codewords,
+                exl3_stream_t stream)
+{
+    if (!trellis || !codewords) return EXL3_E_NULL;
+    if (k < 1 || k > 8) return EXL3_E_K;
+    if (n_tiles < 0) return EXL3_E_SHAPE;
+    if (!aligned(trellis, 4) || !aligned(codewords, 16)) return EXL3_E_ALIGN;
+    if (n_tiles == 0) return EXL3_OK;
+    return launch_unpack(reinterpret_cast<const uint32_t*>(trellis), n_tiles, k, codewords,
+                         (cudaStream_t)stream);
+}
+
+int exl3_decode(const uint16_t* trellis, int64_t t_in, int64_t t_out, int k, int cb, int64_t tn0,
+                int64_t tn_count, uint16_t* w, int64_t ld, exl3_stream_t stream)
+{
+    if (!trellis || !w) return EXL3_E_NULL;
+    if (k < 1 || k > 8) return EXL3_E_K;
+    if (cb < 0 || cb > 2) return EXL3_E_CODEBOOK;
+    if (t_in < 0 || t_out < 0 || tn_count < 0) return EXL3_E_SHAPE;
+    if (tn0 < 0 || tn0 + tn_count > t_out || ld < 16 * tn_count) return EXL3_E_RANGE;
+    if (!aligned(trellis, 4)) return EXL3_E_ALIGN;
+    if (t_in == 0 || tn_count == 0) return EXL3_OK;
+    return launch_decode(reinterpret_cast<const uint32_t*>(trellis), t_in, t_out, k, cb, tn0,
+                         tn_count, reinterpret_cast<__half*>(w), ld, (cudaStream_t)stream);
+}
+
+int exl3_codebook_table(int cb, uint16_t* table65536, exl3_stream_t stream)
+{
+    if (!table65536) return EXL3_E_NULL;
+    if (cb < 0 || cb > 2) return EXL3_E_CODEBOOK;
+    return launch_table(cb, reinterpret_cast<__half*>(table65536), (cudaStream_t)stream);
+}
+
+static int check_dtype_align(const void* x, int x_dtype, int64_t stride)
+{
+    switch (x_dtype) {
+        case EXL3_DT_F16:
+        case EXL3_DT_BF16:
+            if (!aligned(x, 8) || stride % 4) return EXL3_E_ALIGN;
+            return EXL3_OK;
+        case EXL3_DT_F32:
+            if (!aligned(x, 16) || stride % 4) return EXL3_E_ALIGN;
+            return EXL3_OK;
+        default: return EXL3_E_DTYPE;
+    }
+}
+
+int exl3_hadamard128(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
+                     const uint16_t* pre, const uint16_t* post, uint16_t* out, exl3_stream_t stream)
+{
+    if (!x || !out) return EXL3_E_NULL;
+    if (rows < 0 || n <= 0 || n % 128) return EXL3_E_SHAPE;
+    if (x_row_stride < n) return EXL3_E_SHAPE;
+    int rc = check_dtype_align(x, x_dtype, x_row_stride);
+    if (rc) return rc;
+    if (!aligned(out, 8) || (pre && !aligned(pre, 8)) || (post && !aligned(post, 8))) return EXL3_E_ALIGN;
+    if (rows == 0) return EXL3_OK;
+    return launch_hadamard(x, x_dtype, rows, n, x_row_stride, reinterpret_cast<const __half*>(pre),
+                           reinterpret_cast<const __half*>(post), reinterpret_cast<__half*>(out),
+                           nullptr, nullptr, nullptr, false, (cudaStream_t)stream);
+}
+
+size_t exl3_workspace_bytes(int64_t max_rows, int64_t max_in)
+{
+    if (max_rows < 1) max_rows = 1;
+    if (max_in < 128) max_in = 128;
+    const int64_t rows_per_block = max_rows < 16 ? max_rows : 16;
+    size_t b = kWsPartials + ws_partial_bytes(rows_per_block);
+    b += (size_t)max_rows * (size_t)max_in * 2;  // rotated activations
+    return (b + 255) & ~(size_t)255;
+}
+
+int exl3_workspace_init(void* workspace, size_t bytes, exl3_stream_t stream)
+{
+    if (!workspace) return EXL3_E_NULL;
+    if (bytes < kWsPartials) return EXL3_E_WORKSPACE;
+    if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
+    return note_cuda(cudaMemsetAsync(workspace, 0, kWsPartials, (cudaStream_t)stream));
+}
+
+int exl3_workspace_status(const void* workspace, int* status_out, exl3_stream_t stream)
+{
+    if (!workspace || !status_out) return EXL3_E_NULL;
+    cudaError_t e = cudaMemcpyAsync(status_out, workspace, sizeof(int), cudaMemcpyDeviceToHost,
+                                    (cudaStream_t)stream);
+    if (e != cudaSuccess) return note_cuda(e);
+    return note_cuda(cudaStreamSynchronize((cudaStream_t)stream));
+}
+
+int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const uint16_t* trellis,
+              int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
+              const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
+              size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+{
+    if (!x || !trellis || !y) return EXL3_E_NULL;
+    if (k < 1 || k > 8) return EXL3_E_K;
+    if (cb < 0 || cb > 2) return EXL3_E_CODEBOOK;
+    if (t_in <= 0 || t_out <= 0 || t_in % 8 || t_out % 8) return EXL3_E_SHAPE;
+    if (t_out / 8 > kMaxCounters || t_in > (1 << 24) || t_out > (1 << 24)) return EXL3_E_SHAPE;
+    if (rows < 1 || rows > 16) return EXL3_E_ROWS;
+    const int64_t in = 16 * t_in, out = 16 * t_out;
+    if (x_row_stride < in || y_row_stride < out) return EXL3_E_SHAPE;
+    int rc = check_dtype_align(x, x_dtype, x_row_stride);
+    if (rc) return rc;
+    if (!aligned(trellis, 16) || !aligned(y, 8) || y_row_stride % 4) return EXL3_E_ALIGN;
+    if ((suh && !aligned(suh, 8)) || (svh && !aligned(svh, 8)) || (bias && !aligned(bias, 8)))
+        return EXL3_E_ALIGN;
+    if (!workspace) return EXL3_E_WORKSPACE;
+    if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
+    const size_t need = kWsPartials + ws_partial_bytes(rows) + (size_t)rows * in * 2;
+    if (workspace_bytes < need) return EXL3_E_WORKSPACE;
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    __half* xh = reinterpret_cast<__half*>(ws + kWsPartials + ws_partial_bytes(rows));
+    const bool pdl = (flags & EXL3_FLAG_PDL) != 0;
+    cudaStream_t s = (cudaStream_t)stream;
+
+    rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
+                         nullptr, xh, nullptr, nullptr, nullptr, pdl, s);
+    if (rc) return rc;
+
+    GemvArgs a = {};
+    a.trellis = reinterpret_cast<const uint32_t*>(trellis);
+    a.xh = xh;
+    a.svh = reinterpret_cast<const __half*>(svh);
+    a.bias = reinterpret_cast<const __half*>(bias);
+    a.y = reinterpret_cast<__half*>(y);
+    a.blocks = nullptr;
+    a.partials = reinterpret_cast<float*>(ws + kWsPartials);
+    a.counters = reinterpret_cast<unsigned*>(ws + kWsCounters);
+    a.status = reinterpret_cast<int*>(ws + kWsStatus);
+    a.y_row_stride = y_row_stride;
+    a.t_in = (int)t_in;
+    a.t_out_total = (int)t_out;
+    a.ncb = (int)(t_out / 8);
+    a.rows = rows;
+    a.raw_out = 0;
+    return launch_gemv(a, k, cb, pdl, s);
+}
+
+/* Tuning hook used by the benchmark sweeps: CTAs per SM (1 or 2) and the dynamic
+ * shared-memory budget per CTA of the streamed GEMV.  Not part of the stable ABI. */
+EXL3_API void exl3_tune_gemv(int ctas_per_sm, int smem_budget_bytes)
+{
+    gemv_set_tuning(ctas_per_sm, smem_budget_bytes);
+}
+
+}  // extern "C"

@@ -1,0 +1,72 @@
+// Internal C++ interface between the translation units of libexl3b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/exl3_b200.h"
+#include "exl3_device.cuh"
+
+namespace exl3 {
+
+// ---- host helpers (exl3_capi.cu) -------------------------------------------------------------
+int device_sm_count();              // SM count of the current device (cached per device)
+int note_cuda(cudaError_t e);       // records the error text; returns EXL3_OK or EXL3_E_CUDA
+int check_launch();                 // note_cuda(cudaGetLastError())
+
+// ---- workspace layout ------------------------------------------------------------------------
+// [0, 256)                status word + padding
+// [256, 256 + 32 KiB)     per-column-block arrival counters (zero between launches)
+// [kWsPartials, ...)      split-K partial sums: kMaxCtas x 2 segments x rows x 128 floats
+// [...]                   rotated activations xh: rows x in fp16
+constexpr size_t kWsStatus = 0;
+constexpr size_t kWsCounters = 256;
+constexpr int kMaxCounters = 8192;
+constexpr size_t kWsPartials = kWsCounters + (size_t)kMaxCounters * 4;
+constexpr int kMaxCtas = 1024;
+
+inline size_t ws_partial_bytes(int64_t rows_per_block)
+{
+    return (size_t)kMaxCtas * 2 * (size_t)rows_per_block * 128 * sizeof(float);
+}
+
+// ---- launchers -------------------------------------------------------------------------------
+int launch_unpack(const uint32_t* trellis, int64_t n_tiles, int k, uint16_t* out, cudaStream_t s);
+int launch_decode(const uint32_t* trellis, int64_t t_in, int64_t t_out, int k, int cb, int64_t tn0,
+                  int64_t tn_count, __half* w, int64_t ld, cudaStream_t s);
+int launch_table(int cb, __half* table, cudaStream_t s);
+int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
+                    const __half* pre, const __half* post, __half* out, const int32_t* row_src,
+                    const int32_t* pre_row, const int32_t* post_row, bool pdl, cudaStream_t s);
+
+// One logical 128-column output block of a streamed GEMV: where its weights, activations,
+// output scales and results live.  NULL descriptor table = the identity mapping of a plain
+// linear layer.
+struct ColBlock {
+    int32_t phys;      // column-block index inside the trellis (tile column = 8 * phys)
+    int32_t xrow;      // first row of xh this block multiplies
+    int32_t sv_off;    // element offset into svh / bias (multiple of 128), -1 = none
+    int32_t y_off;     // element offset of the block's 128 outputs inside a y row
+};
+
+struct GemvArgs {
+    const uint32_t* trellis;   // (t_in, t_out_total, 8K) words
+    const __half* xh;          // rotated activations, rows of `in` halves
+    const __half* svh;         // may be NULL
+    const __half* bias;        // may be NULL
+    __half* y;
+    const ColBlock* blocks;    // may be NULL
+    float* partials;
+    unsigned* counters;
+    int* status;
+    int64_t y_row_stride;
+    int t_in;                  // input tiles (multiple of 8)
+    int t_out_total;           // tile columns of the trellis tensor
+    int ncb;                   // logical 128-column blocks to compute
+    int rows;                  // activation rows per block (1..16)
+    int stages;                // depth of the shared-memory ring
+    int raw_out;               // 1: write fp16(y_inner) without rotation (MoE gate/up)
+};
+
+int launch_gemv(const GemvArgs& a, int k, int cb, bool pdl, cudaStream_t s);
+
+}  // namespace exl3

@@ -1,0 +1,168 @@
+"""Functional CUDA twins of the reference's codec primitives, on torch tensors.
+
+Each function takes CUDA tensors, validates like the reference's numpy function of
+the same name (``ValueError`` on bad shapes), and calls the C ABI with raw device
+pointers on the current stream.  PyTorch is only the owner of device memory here.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import DT_BF16, DT_F16, DT_F32
+
+_DTYPES = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32}
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _need_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: the EXL3 path has no CPU implementation")
+
+
+def as_u16(t: torch.Tensor) -> torch.Tensor:
+    """int16 / uint16 storage of packed trellis words (bit pattern is what matters)."""
+    if t.dtype in (torch.int16, torch.uint16):
+        return t
+    raise ValueError(f"packed trellis must be (u)int16, got {t.dtype}")
+
+
+class Workspace:
+    """Per-device scratch for the matmul entry points: split-K partial sums, arrival
+    counters, the status word and the rotated activations.  One per device, grown on
+    demand; calls that share it are ordered by the stream they run on."""
+
+    _per_device: dict[int, "Workspace"] = {}
+
+    def __init__(self, device: torch.device, max_rows: int, max_in: int):
+        lib = _lib.load()
+        self.device = device
+        self.max_rows, self.max_in = max_rows, max_in
+        self.nbytes = int(lib.exl3_workspace_bytes(max_rows, max_in))
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        _lib.check(lib.exl3_workspace_init(self.buf.data_ptr(), self.nbytes, _stream(device)),
+                   "exl3_workspace_init")
+
+    @classmethod
+    def get(cls, device: torch.device, rows: int, in_features: int) -> "Workspace":
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        ws = cls._per_device.get(idx)
+        if ws is None or ws.max_rows < rows or ws.max_in < in_features:
+            if ws is not None:
+                torch.cuda.current_stream(device).synchronize()
+            ws = Workspace(torch.device("cuda", idx), max(rows, ws.max_rows if ws else 16),
+                           max(in_features, ws.max_in if ws else 32768))
+            cls._per_device[idx] = ws
+        return ws
+
+    def status(self) -> int:
+        import ctypes
+        out = ctypes.c_int(0)
+        _lib.check(_lib.load().exl3_workspace_status(self.buf.data_ptr(), ctypes.byref(out),
+                                                     _stream(self.device)), "exl3_workspace_status")
+        return out.value
+
+
+def unpack_trellis(packed: torch.Tensor, k: int) -> torch.Tensor:
+    """(tiles_k, tiles_n, 16K) packed words -> (tiles_k, tiles_n, 256) int16 codewords
+    (ponyexl3/ref/trellis.py:205-214)."""
+    _need_cuda(packed, "packed")
+    if packed.ndim != 3:
+        raise ValueError(f"expected 3D packed trellis, got {tuple(packed.shape)}")
+    if not 1 <= k <= 8:
+        raise ValueError(f"K must be in [1, 8], got {k}")
+    if packed.shape[-1] != 16 * k:
+        raise ValueError(f"expected last dim {16 * k}, got {packed.shape[-1]}")
+    packed = as_u16(packed).contiguous()
+    out = torch.empty(packed.shape[:2] + (256,), dtype=torch.int16, device=packed.device)
+    n = packed.shape[0] * packed.shape[1]
+    _lib.check(_lib.load().exl3_unpack(packed.data_ptr(), n, k, out.data_ptr(),
+                                       _stream(packed.device)), "exl3_unpack")
+    return out
+
+
+def decode_packed_trellis(trellis: torch.Tensor, k: int, cb: int, *, n_offset: int = 0,
+                          n_count: int | None = None) -> torch.Tensor:
+    """Inner weight matrix (in, n_count) fp16 of a packed trellis, bit-exact with the
+    reference (ponyexl3/ref/decode.py:32-81).  For tests and debugging only."""
+    _need_cuda(trellis, "trellis")
+    if trellis.ndim != 3:
+        raise ValueError("trellis must be 3D")
+    t_in, t_out, ps = trellis.shape
+    if not 1 <= k <= 8:
+        raise ValueError(f"K must be in [1, 8], got {k}")
+    if ps != 16 * k:
+        raise ValueError(f"packed size {ps} != expected {16 * k} for K={k}")
+    if n_offset % 128 != 0:
+        raise ValueError("n_offset must be divisible by 128")
+    n_count = t_out * 16 - n_offset if n_count is None else n_count
+    if n_count % 16 or n_offset + n_count > t_out * 16:
+        raise ValueError("slice exceeds output features")
+    trellis = as_u16(trellis).contiguous()
+    w = torch.empty((t_in * 16, n_count), dtype=torch.float16, device=trellis.device)
+    _lib.check(_lib.load().exl3_decode(trellis.data_ptr(), t_in, t_out, k, int(cb), n_offset // 16,
+                                       n_count // 16, w.data_ptr(), n_count,
+                                       _stream(trellis.device)), "exl3_decode")
+    return w
+
+
+def codebook_table(cb: int, device: torch.device | str = "cuda") -> torch.Tensor:
+    """decode_3inst of every 16-bit codeword (ponyexl3/ref/codebook.py:66-91)."""
+    device = torch.device(device)
+    t = torch.empty(65536, dtype=torch.float16, device=device)
+    _lib.check(_lib.load().exl3_codebook_table(int(cb), t.data_ptr(), _stream(device)),
+               "exl3_codebook_table")
+    return t
+
+
+def had_r_128(x: torch.Tensor, *, pre_scale: torch.Tensor | None = None,
+              post_scale: torch.Tensor | None = None) -> torch.Tensor:
+    """fp16( ((x * pre) @ H128/sqrt(128)) * post ) along the last dimension
+    (ponyexl3/ref/hadamard.py:50-80); x fp16 / bf16 / fp32, 2-D."""
+    _need_cuda(x, "x")
+    if x.ndim != 2:
+        raise ValueError("had_r_128 expects 2D input (rows, features)")
+    if x.shape[1] % 128 != 0:
+        raise ValueError(f"feature dim {x.shape[1]} not divisible by 128")
+    if x.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {x.dtype}")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    pre = None if pre_scale is None else pre_scale.to(torch.float16).contiguous()
+    post = None if post_scale is None else post_scale.to(torch.float16).contiguous()
+    out = torch.empty(x.shape, dtype=torch.float16, device=x.device)
+    _lib.check(_lib.load().exl3_hadamard128(
+        x.data_ptr(), _DTYPES[x.dtype], x.shape[0], x.shape[1], x.stride(0),
+        None if pre is None else pre.data_ptr(), None if post is None else post.data_ptr(),
+        out.data_ptr(), _stream(x.device)), "exl3_hadamard128")
+    return out
+
+
+def gemv(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh: torch.Tensor | None,
+         svh: torch.Tensor | None, bias: torch.Tensor | None, *, pdl: bool = False,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """The whole linear forward for 1..16 rows in two launches (rotation, streamed GEMV).
+    x2d (rows, in) fp16/bf16/fp32 -> (rows, out) fp16."""
+    _need_cuda(x2d, "x")
+    rows, in_features = x2d.shape
+    t_in, t_out, _ = trellis.shape
+    if in_features != t_in * 16:
+        raise ValueError(f"x has {in_features} features, layer expects {t_in * 16}")
+    if x2d.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {x2d.dtype}")
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    ws = Workspace.get(x2d.device, rows, in_features)
+    y = out if out is not None else torch.empty((rows, t_out * 16), dtype=torch.float16,
+                                                device=x2d.device)
+    _lib.check(_lib.load().exl3_gemv(
+        x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out,
+        k, int(cb), None if suh is None else suh.data_ptr(),
+        None if svh is None else svh.data_ptr(), None if bias is None else bias.data_ptr(),
+        y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes, _lib.FLAG_PDL if pdl else 0,
+        _stream(x2d.device)), "exl3_gemv")
+    return y
