@@ -57,6 +57,11 @@ extern "C" {
 #define EXL3_FLAG_PDL 1u        /* launch with programmatic stream serialisation so the next
                                    kernel's weight prefetch overlaps this kernel's tail */
 
+#define EXL3_FLAG_FAST_ACCUM 2u /* 3INST / MCG only: keep the two fp16 halves of a codebook value
+                                   apart and let the fp32 tensor-core accumulation add them,
+                                   instead of rounding their sum to fp16 first.  Saves one
+                                   instruction per weight; outputs move by < 2e-4 relative */
+
 typedef void* exl3_stream_t;    /* cudaStream_t */
 
 EXL3_API int exl3_version(void);

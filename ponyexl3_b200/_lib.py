@@ -17,6 +17,7 @@ LIB_PATH = _PKG / "lib" / "libexl3b200.so"
 
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 FLAG_PDL = 1
+FLAG_FAST_ACCUM = 2
 
 E_CUDA = -9
 _VALUE_ERRORS = {-1, -2, -3, -4, -5, -6, -7, -8, -10, -11}

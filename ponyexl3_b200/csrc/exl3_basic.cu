@@ -91,10 +91,12 @@ __global__ void __launch_bounds__(256)
                     const __half* __restrict__ pre, const __half* __restrict__ post,
                     __half* __restrict__ out, const int32_t* __restrict__ row_src,
                     const int32_t* __restrict__ pre_row, const int32_t* __restrict__ post_row,
-                    int wait_dependency)
+                    int wait_dependency, int out_mode)
 {
-    if (wait_dependency) griddep_wait();
+    // Let the next kernel of the stream (the GEMV that consumes `out`) start streaming its
+    // weights right away; it waits for this grid before it reads any activation.
     griddep_launch_dependents();
+    if (wait_dependency) griddep_wait();
     const int lane = threadIdx.x & 31;
     const int64_t nblk = n >> 7;
     const int64_t total = rows * nblk;
@@ -127,7 +129,20 @@ __global__ void __launch_bounds__(256)
         uint2 o;
         o.x = h2_as_u32(__floats2half2_rn(v[0], v[1]));
         o.y = h2_as_u32(__floats2half2_rn(v[2], v[3]));
-        *reinterpret_cast<uint2*>(out + r * n + col) = o;
+        if (out_mode == HAD_OUT_F16) {
+            *reinterpret_cast<uint2*>(out + r * n + col) = o;
+        } else {
+            // one 32-bit word per element for the GEMV's two-slot fragments:
+            // (x, 0) keeps exactly-decoded weights, (x, x) lets the MMA add the two
+            // codebook halves itself
+            uint4 e;
+            const uint32_t m = (out_mode == HAD_OUT_PAIR_X0) ? 0u : 0x00010000u;
+            e.x = (o.x & 0xFFFFu) * (1u + m);
+            e.y = (o.x >> 16) * (1u + m);
+            e.z = (o.y & 0xFFFFu) * (1u + m);
+            e.w = (o.y >> 16) * (1u + m);
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + r * n + col) = e;
+        }
     }
 }
 
@@ -206,7 +221,8 @@ int launch_table(int cb, __half* table, cudaStream_t s)
 
 int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
                     const __half* pre, const __half* post, __half* out, const int32_t* row_src,
-                    const int32_t* pre_row, const int32_t* post_row, bool pdl, cudaStream_t s)
+                    const int32_t* pre_row, const int32_t* post_row, bool pdl, int out_mode,
+                    cudaStream_t s)
 {
     const int g = grid_for(rows * (n >> 7), 8);
     cudaLaunchConfig_t cfg = {};
@@ -224,16 +240,16 @@ int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t
     switch (x_dtype) {
         case EXL3_DT_F16:
             e = cudaLaunchKernelEx(&cfg, hadamard_kernel<__half>, (const __half*)x, rows, n,
-                                   x_row_stride, pre, post, out, row_src, pre_row, post_row, wait);
+                                   x_row_stride, pre, post, out, row_src, pre_row, post_row, wait, out_mode);
             break;
         case EXL3_DT_BF16:
             e = cudaLaunchKernelEx(&cfg, hadamard_kernel<__nv_bfloat16>, (const __nv_bfloat16*)x,
                                    rows, n, x_row_stride, pre, post, out, row_src, pre_row, post_row,
-                                   wait);
+                                   wait, out_mode);
             break;
         case EXL3_DT_F32:
             e = cudaLaunchKernelEx(&cfg, hadamard_kernel<float>, (const float*)x, rows, n,
-                                   x_row_stride, pre, post, out, row_src, pre_row, post_row, wait);
+                                   x_row_stride, pre, post, out, row_src, pre_row, post_row, wait, out_mode);
             break;
         default: return EXL3_E_DTYPE;
     }

@@ -72,6 +72,58 @@ template <int K> EXL3_HD void lane_codewords(uint32_t a, uint32_t b, uint32_t c,
     }
 }
 
+// Byte permute of the register pair (b:a) — selector nibble i picks the source byte of
+// result byte i (0-3 from a, 4-7 from b).
+EXL3_HD uint32_t byte_perm(uint32_t a, uint32_t b, uint32_t sel)
+{
+#if defined(__CUDA_ARCH__)
+    return __byte_perm(a, b, sel);
+#else
+    const uint64_t v = ((uint64_t)b << 32) | a;
+    uint32_t r = 0;
+    for (int i = 0; i < 4; i++) r |= (uint32_t)((v >> (8 * ((sel >> (4 * i)) & 7))) & 0xFF) << (8 * i);
+    return r;
+#endif
+}
+
+// 64-bit a * b + (c_hi << 32), returned as (lo, hi).  On the device this is one
+// mad.wide.u32, which runs on the integer-multiply pipe and so shifts a word without
+// touching the (half-rate) logic/shift pipe.
+EXL3_HD void mad_wide(uint32_t a, uint32_t b, uint32_t c_hi, uint32_t& lo, uint32_t& hi)
+{
+#if defined(__CUDA_ARCH__)
+    uint64_t r;
+    const uint64_t c = (uint64_t)c_hi << 32;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"(a), "r"(b), "l"(c));
+    lo = (uint32_t)r;
+    hi = (uint32_t)(r >> 32);
+#else
+    const uint64_t r = (uint64_t)a * b + ((uint64_t)c_hi << 32);
+    lo = (uint32_t)r;
+    hi = (uint32_t)(r >> 32);
+#endif
+}
+
+// K = 4: lane t owns word t of the tile and needs the low 12 bits of word t-1 (its halo).
+// With V = (halo : w) as a 44-bit value, codeword j is V >> (28 - 4j) & 0xFFFF.  Odd j are
+// byte-aligned in V, even j in V << 4 (one wide multiply); every window is then one byte
+// permute with zero fill, and the top one falls out of the wide multiply for free:
+// 9 logic-pipe operations for 8 codewords instead of 16 shifts and masks.
+EXL3_HD void lane_codewords_k4(uint32_t w, uint32_t prev, uint32_t (&cw)[8])
+{
+    const uint32_t p = prev & 0xFFFu;
+    uint32_t lo4, hi4;
+    mad_wide(w, 16u, p * 16u, lo4, hi4);       // (hi4 : lo4) = V << 4, hi4 < 2^16
+    cw[7] = byte_perm(w, 0u, 0x4410);
+    cw[5] = byte_perm(w, 0u, 0x4421);
+    cw[3] = byte_perm(w, 0u, 0x4432);
+    cw[1] = byte_perm(w, p, 0x6643);            // w byte 3, halo byte 0, zero, zero
+    cw[6] = byte_perm(lo4, 0u, 0x4421);
+    cw[4] = byte_perm(lo4, 0u, 0x4432);
+    cw[2] = byte_perm(lo4, hi4, 0x6643);
+    cw[0] = hi4;
+}
+
 // Integer part of the codebooks (reference: ponyexl3/ref/codebook.py:66-91).
 // 3INST and MCG: a 32-bit word whose two fp16 halves sum to the weight.
 // MUL1: the fp16 bit pattern 0x6400 + (sum of the product's bytes), to be sent

@@ -1,13 +1,60 @@
 // extern "C" surface of libexl3b200.so: argument validation on the host, then the
 // kernel launchers.  No allocation, no global mutable state beyond per-device
 // caches of immutable facts (SM count, function attributes).
+#include <stdio.h>
 #include <string.h>
 
 #include "exl3_internal.h"
+#include "exl3_tma.h"
 
 namespace exl3 {
 
+char* g_cuda_err_buf();
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base,
+                    const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                    CUtensorMapSwizzle swizzle)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return EXL3_E_CUDA;
+    cuuint64_t gdim[5], gstr[5];
+    cuuint32_t bdim[5], estr[5];
+    for (int i = 0; i < rank; i++) {
+        gdim[i] = dims[i];
+        bdim[i] = box[i];
+        estr[i] = 1;
+        if (i + 1 < rank) gstr[i] = strides_bytes[i];
+    }
+    CUresult r = fn(map, dtype, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_cuda_err_buf(), 256, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return EXL3_E_CUDA;
+    }
+    return EXL3_OK;
+}
+
 static thread_local char g_cuda_err[256] = "";
+char* g_cuda_err_buf() { return g_cuda_err; }
 
 int note_cuda(cudaError_t e)
 {
@@ -125,7 +172,7 @@ int exl3_hadamard128(const void* x, int x_dtype, int64_t rows, int64_t n, int64_
     if (rows == 0) return EXL3_OK;
     return launch_hadamard(x, x_dtype, rows, n, x_row_stride, reinterpret_cast<const __half*>(pre),
                            reinterpret_cast<const __half*>(post), reinterpret_cast<__half*>(out),
-                           nullptr, nullptr, nullptr, false, (cudaStream_t)stream);
+                           nullptr, nullptr, nullptr, false, HAD_OUT_F16, (cudaStream_t)stream);
 }
 
 size_t exl3_workspace_bytes(int64_t max_rows, int64_t max_in)
@@ -134,7 +181,7 @@ size_t exl3_workspace_bytes(int64_t max_rows, int64_t max_in)
     if (max_in < 128) max_in = 128;
     const int64_t rows_per_block = max_rows < 16 ? max_rows : 16;
     size_t b = kWsPartials + ws_partial_bytes(rows_per_block);
-    b += (size_t)max_rows * (size_t)max_in * 2;  // rotated activations
+    b += (size_t)max_rows * (size_t)max_in * 4;  // rotated activations, one word per element
     return (b + 255) & ~(size_t)255;
 }
 
@@ -175,16 +222,18 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
         return EXL3_E_ALIGN;
     if (!workspace) return EXL3_E_WORKSPACE;
     if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
-    const size_t need = kWsPartials + ws_partial_bytes(rows) + (size_t)rows * in * 2;
+    const size_t need = kWsPartials + ws_partial_bytes(rows) + (size_t)rows * in * 4;
     if (workspace_bytes < need) return EXL3_E_WORKSPACE;
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    __half* xh = reinterpret_cast<__half*>(ws + kWsPartials + ws_partial_bytes(rows));
+    uint32_t* xh = reinterpret_cast<uint32_t*>(ws + kWsPartials + ws_partial_bytes(rows));
     const bool pdl = (flags & EXL3_FLAG_PDL) != 0;
+    const bool fast = (flags & EXL3_FLAG_FAST_ACCUM) != 0 && cb != CB_MUL1;
     cudaStream_t s = (cudaStream_t)stream;
 
     rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
-                         nullptr, xh, nullptr, nullptr, nullptr, pdl, s);
+                         nullptr, reinterpret_cast<__half*>(xh), nullptr, nullptr, nullptr, pdl,
+                         fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s);
     if (rc) return rc;
 
     GemvArgs a = {};
@@ -202,7 +251,9 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     a.t_out_total = (int)t_out;
     a.ncb = (int)(t_out / 8);
     a.rows = rows;
+    a.x_rows_total = rows;
     a.raw_out = 0;
+    a.fast_accum = fast ? 1 : 0;
     return launch_gemv(a, k, cb, pdl, s);
 }
 

@@ -6,15 +6,28 @@
 // SM) and CTA i takes the contiguous item range [N*i/G, N*(i+1)/G), so every CTA
 // streams the same number of bytes whatever the layer shape.
 //
-// Inside a CTA one producer lane feeds a shared-memory ring with the bulk-copy
-// engine (cp.async.bulk, completion counted on mbarriers): eight contiguous
-// 256*K-byte tile rows plus the item's 128 rotated activations per row.  Weight
-// copies of the first ring fill are issued BEFORE the programmatic-launch wait, so
-// under EXL3_FLAG_PDL a layer's weights stream while the previous kernel drains.
-// Eight consumer warps each own one 16-column tile column of the block: a lane
-// reads the 2-3 words holding its eight codewords, cuts the 16-bit windows, runs
-// the codebook in registers and feeds mma.sync m16n8k16 (the packed tile order is
-// the A-fragment order of W^T), accumulating in fp32.
+// Inside a CTA one producer lane feeds a shared-memory ring with TMA tensor copies
+// (completion counted on mbarriers): ONE 3-D box per item for the 8x8 packed tiles
+// and ONE 128B-swizzled 3-D box for the item's 128 rotated activations of every row.
+// (Issuing the eight tile rows as separate bulk copies made the single producer lane
+// the bottleneck: a copy instruction costs tens of cycles to issue.)  Weight copies
+// of the first ring fill are issued BEFORE the programmatic-launch wait, so under
+// EXL3_FLAG_PDL a layer's weights stream while the previous kernel drains.
+//
+// Eight consumer warps; warp w owns tile columns 2*(w&3), 2*(w&3)+1 of the block and
+// the k-half (w>>2) of the item, so one activation fragment load serves two tiles.
+// The decode is bound by the half-rate logic pipe of the SM (64 lanes/clk: LOP3, PRMT;
+// shifts run at a quarter), so the inner loop is written to spend exactly two logic
+// operations per weight at K = 4 — one byte-permute to cut the codeword window, one
+// LOP3 for the codebook mask — and pushes everything else to other pipes: shifts
+// become wide integer multiplies, and the two fp16 halves of a 3INST value are added
+// by HADD2 with broadcast operands straight into a (w, w) register.  Each weight thus
+// occupies both k-slots of a 32-bit A-fragment register of mma.sync m16n8k16 and the
+// activations arrive as (x, 0) words, which costs a second MMA per tile on the
+// otherwise idle tensor pipe instead of byte-permutes on the saturated one.
+// With EXL3_FLAG_FAST_ACCUM the HADD2 is skipped: the register keeps the two halves
+// (lo, hi), the activations arrive as (x, x), and the MMA adds lo*x + hi*x in fp32
+// (weights then differ from the reference's fp16-rounded sum by under 2^-11 relative).
 //
 // A column block whose k-range is split over several CTAs is finished by the last
 // CTA to arrive (partial sums in the workspace, one atomic counter per block, no
@@ -23,27 +36,28 @@
 #include <algorithm>
 
 #include "exl3_internal.h"
+#include "exl3_tma.h"
 
 namespace exl3 {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kGemvThreads = kConsumerThreads + 32;
-constexpr int kXRowBytes = 272;      // 128 halves + 16 bytes so the 8 rows of a fragment hit 8 banks
 constexpr int kYStride = 132;
 constexpr int kMaxStages = 16;
 constexpr int kHeaderBytes = 512;
 
 template <int K, int NMMA> struct GemvLayout {
     static constexpr int kTileWords = 8 * K;
-    static constexpr int kRowBytes = 8 * kTileWords * 4;          // one tile row of the item
-    static constexpr int kWeightBytes = 8 * kRowBytes;            // 2048 * K
-    static constexpr int kXBytes = NMMA * 8 * kXRowBytes;
-    static constexpr int kStageBytes = kWeightBytes + kXBytes;
-    static constexpr int kYBytes = NMMA * 8 * kYStride * 4;
-    static constexpr int kStage0 = kHeaderBytes + kYBytes;
-    static_assert(kStage0 % 128 == 0 && kStageBytes % 16 == 0, "bulk copies need 16-byte alignment");
+    static constexpr int kWeightBytes = 64 * kTileWords * 4;      // 8x8 tiles: 2048 * K
+    static constexpr int kYBytes = 2 * NMMA * 8 * kYStride * 4;   // one copy per k-half
+    static constexpr int kStage0 = (kHeaderBytes + kYBytes + 1023) / 1024 * 1024;
 };
+
+// Activations of one item in shared memory: 4 quarters of 32 k-values, each `rows`
+// lines of 128 bytes (32 words of (x, 0) or (x, x)); the TMA engine XOR-swizzles the
+// 16-byte chunk index with the 128-byte line index (128B swizzle).
+__host__ __device__ inline int x_stage_bytes(int rows) { return (4 * rows * 128 + 1023) / 1024 * 1024; }
 
 __device__ __forceinline__ int64_t item_begin(int64_t n_items, int cta, int grid)
 {
@@ -55,11 +69,26 @@ __device__ __forceinline__ int item_owner(int64_t n_items, int64_t i, int grid)
     return (int)(((i + 1) * grid - 1) / n_items);
 }
 
-template <int K, int CB, int NMMA>
-__global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvArgs a)
+// (w, w) from the two-halves word of 3INST / MCG, or from the MUL1 pattern.
+template <int CB, bool FAST> __device__ __forceinline__ uint32_t weight_slot_pair(uint32_t cw)
+{
+    const uint32_t r = codebook_word<CB>(cw);
+    if (CB == CB_MUL1) {
+        const __half2 h = u32_as_h2(r * 0x00010001u);
+        return h2_as_u32(__hfma2(h, u32_as_h2(0x1EEE1EEEu), u32_as_h2(0xC931C931u)));
+    }
+    if (FAST) return r;
+    const __half2 h = u32_as_h2(r);
+    return h2_as_u32(__hadd2(__low2half2(h), __high2half2(h)));
+}
+
+template <int K, int CB, int NMMA, bool FAST>
+__global__ void __launch_bounds__(kGemvThreads, 2)
+    gemv_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap tm_w,
+                const __grid_constant__ CUtensorMap tm_x)
 {
     using L = GemvLayout<K, NMMA>;
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
     volatile int* s_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
@@ -73,7 +102,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvArgs a)
     const int64_t it_begin = item_begin(n_items, cta, grid);
     const int nitems = (int)(item_begin(n_items, cta + 1, grid) - it_begin);
     const int ns = a.stages;
-    const int in_features = a.t_in * 16;
+    const int xbytes = x_stage_bytes(a.rows);
+    const int stage_bytes = xbytes + L::kWeightBytes;
 
     if (tid == 0) {
         for (int s = 0; s < ns; s++) {
@@ -89,31 +119,24 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvArgs a)
     // ------------------------------------------------------------------ producer ----
     if (warp == kConsumerWarps) {
         if (lane != 0) return;
-        const uint32_t tx = L::kWeightBytes + (uint32_t)a.rows * 256u;
+        const uint32_t tx = L::kWeightBytes + (uint32_t)a.rows * 512u;
+        tma_prefetch_desc(&tm_w);
+        tma_prefetch_desc(&tm_x);
         auto issue_weights = [&](int li) {
             const int64_t it = it_begin + li;
             const int cb = (int)(it / nkb), kb = (int)(it % nkb);
             const int phys = a.blocks ? a.blocks[cb].phys : cb;
             const int s = li % ns;
-            const uint32_t bar = smem_u32(&full[s]);
-            const uint32_t dst = smem_u32(stage0 + (size_t)s * L::kStageBytes);
-            const uint32_t* src =
-                a.trellis + ((int64_t)(8 * kb) * a.t_out_total + 8 * (int64_t)phys) * L::kTileWords;
-#pragma unroll
-            for (int r = 0; r < 8; r++)
-                bulk_g2s(dst + r * L::kRowBytes, src + (int64_t)r * a.t_out_total * L::kTileWords,
-                         L::kRowBytes, bar);
+            tma_load_3d(smem_u32(stage0 + (size_t)s * stage_bytes + xbytes), &tm_w, 0, 8 * phys,
+                        8 * kb, smem_u32(&full[s]));
         };
         auto issue_x = [&](int li) {
             const int64_t it = it_begin + li;
             const int cb = (int)(it / nkb), kb = (int)(it % nkb);
             const int xrow = a.blocks ? a.blocks[cb].xrow : 0;
             const int s = li % ns;
-            const uint32_t bar = smem_u32(&full[s]);
-            const uint32_t dst = smem_u32(stage0 + (size_t)s * L::kStageBytes + L::kWeightBytes);
-            const __half* src = a.xh + (int64_t)xrow * in_features + 128 * kb;
-            for (int n = 0; n < a.rows; n++)
-                bulk_g2s(dst + n * kXRowBytes, src + (int64_t)n * in_features, 256u, bar);
+            tma_load_3d(smem_u32(stage0 + (size_t)s * stage_bytes), &tm_x, 0, xrow, 4 * kb,
+                        smem_u32(&full[s]));
         };
         // A block table is written by an earlier kernel of the stream: read it only
         // after the dependency wait.  Plain layers prefetch their weights first.
@@ -146,11 +169,33 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvArgs a)
     LaneWords<K> lw;
     lw.init(lane);
     const int g = lane >> 2, tig = lane & 3;
-    float acc[NMMA][4];
+    const int tnp = warp & 3, kh = warp >> 2;
+    const int prev_word = (lane + 31) & 31;
+
+    // Byte offsets of this lane's activation words for the four tile rows of its k-half:
+    // element e = 16*tk + 2*tig (+8 for the second MMA) of the 128-value block sits in
+    // quarter e/32, line `row`, chunk ((e%32)/4) ^ (line & 7), byte 8*(tig&1).
+    int xoff[4][2];
 #pragma unroll
-    for (int m = 0; m < NMMA; m++)
+    for (int tl = 0; tl < 4; tl++)
 #pragma unroll
-        for (int q = 0; q < 4; q++) acc[m][q] = 0.f;
+        for (int h = 0; h < 2; h++) {
+            const int tk = 4 * kh + tl;
+            const int q = tk >> 1;
+            const int chunk = 4 * (tk & 1) + (tig >> 1) + 2 * h;
+            const int line = q * a.rows + g;  // rows of the second MMA group add 8 lines
+            xoff[tl][h] = line * 128 + ((chunk ^ (line & 7)) << 4) + 8 * (tig & 1);
+        }
+
+    float acc[2][NMMA][2][4];
+#pragma unroll
+    for (int t = 0; t < 2; t++)
+#pragma unroll
+        for (int m = 0; m < NMMA; m++)
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int q = 0; q < 4; q++) acc[t][m][h][q] = 0.f;
 
     bool failed = false;
     const int first_cb = (int)(it_begin / nkb);
@@ -165,29 +210,46 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvArgs a)
             if (lane == 0) atomicOr(a.status, ST_WAIT_FULL_TIMEOUT);
         }
         if (!failed) {
-            const uint8_t* st = stage0 + (size_t)s * L::kStageBytes;
-            const uint32_t* wst = reinterpret_cast<const uint32_t*>(st) + warp * L::kTileWords;
-            const uint8_t* xst = st + L::kWeightBytes;
+            const uint8_t* xst = stage0 + (size_t)s * stage_bytes;
+            const uint32_t* wst = reinterpret_cast<const uint32_t*>(xst + xbytes) +
+                                  (4 * kh * 8 + 2 * tnp) * L::kTileWords;
 #pragma unroll
-            for (int tk = 0; tk < 8; tk++) {
-                const uint32_t* tw = wst + tk * 8 * L::kTileWords;
-                const uint32_t wa = tw[lw.i0], wb = tw[lw.i1];
-                const uint32_t wc = LaneWords<K>::kThree ? tw[lw.i2] : 0u;
-                uint32_t cw[8];
-                lane_codewords<K>(wa, wb, wc, lw.sh, cw);
-                uint32_t fa[4];
-                fa[0] = decode_pair<CB>(cw[0], cw[1]);
-                fa[1] = decode_pair<CB>(cw[4], cw[5]);
-                fa[2] = decode_pair<CB>(cw[2], cw[3]);
-                fa[3] = decode_pair<CB>(cw[6], cw[7]);
+            for (int tl = 0; tl < 4; tl++) {
+                // activation fragments: rows g (+8), k-slots of this lane
+                uint2 xb[NMMA][2];
 #pragma unroll
-                for (int m = 0; m < NMMA; m++) {
-                    const int n = g + 8 * m;
-                    const uint32_t* xr =
-                        reinterpret_cast<const uint32_t*>(xst + n * kXRowBytes) + tk * 8 + tig;
-                    const uint32_t b0 = n < a.rows ? xr[0] : 0u;
-                    const uint32_t b1 = n < a.rows ? xr[4] : 0u;
-                    mma_16816(acc[m], fa, b0, b1);
+                for (int m = 0; m < NMMA; m++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        xb[m][h] = make_uint2(0u, 0u);
+                        if (g + 8 * m < a.rows) {
+                            // line index grows by 8 for the second row group: the swizzle
+                            // term (line & 7) is unchanged
+                            xb[m][h] = *reinterpret_cast<const uint2*>(xst + xoff[tl][h] + m * 1024);
+                        }
+                    }
+#pragma unroll
+                for (int t = 0; t < 2; t++) {
+                    const uint32_t* tw = wst + (tl * 8 + t) * L::kTileWords;
+                    uint32_t cw[8];
+                    if (K == 4) {
+                        lane_codewords_k4(tw[lane], tw[prev_word], cw);
+                    } else {
+                        const uint32_t wa = tw[lw.i0], wb = tw[lw.i1];
+                        const uint32_t wc = LaneWords<K>::kThree ? tw[lw.i2] : 0u;
+                        lane_codewords<K>(wa, wb, wc, lw.sh, cw);
+                    }
+                    uint32_t d[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) d[j] = weight_slot_pair<CB, FAST>(cw[j]);
+                    // tile rows 2*tig, 2*tig+1 (codewords 0,4 | 1,5), then rows +8 (2,6 | 3,7)
+                    const uint32_t a1[4] = {d[0], d[4], d[1], d[5]};
+                    const uint32_t a2[4] = {d[2], d[6], d[3], d[7]};
+#pragma unroll
+                    for (int m = 0; m < NMMA; m++) {
+                        mma_16816(acc[t][m][0], a1, xb[m][0].x, xb[m][0].y);
+                        mma_16816(acc[t][m][1], a2, xb[m][1].x, xb[m][1].y);
+                    }
                 }
             }
         }
@@ -197,22 +259,31 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvArgs a)
         if (kb != nkb - 1 && li != nitems - 1) continue;
 
         // ---- end of this CTA's share of column block cb -------------------------------
+        float* yk = ybuf + kh * (NMMA * 8 * kYStride);
 #pragma unroll
-        for (int m = 0; m < NMMA; m++) {
-            float* y0 = ybuf + (2 * tig + 8 * m) * kYStride + 16 * warp + g;
-            y0[0] = acc[m][0];
-            y0[kYStride] = acc[m][1];
-            y0[8] = acc[m][2];
-            y0[kYStride + 8] = acc[m][3];
-            acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-        }
+        for (int t = 0; t < 2; t++)
+#pragma unroll
+            for (int m = 0; m < NMMA; m++) {
+                float* y0 = yk + (2 * tig + 8 * m) * kYStride + 16 * (2 * tnp + t) + g;
+                y0[0] = acc[t][m][0][0] + acc[t][m][1][0];
+                y0[kYStride] = acc[t][m][0][1] + acc[t][m][1][1];
+                y0[8] = acc[t][m][0][2] + acc[t][m][1][2];
+                y0[kYStride + 8] = acc[t][m][0][3] + acc[t][m][1][3];
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int q = 0; q < 4; q++) acc[t][m][h][q] = 0.f;
+            }
         named_bar_sync(1, kConsumerThreads);
+        const float* y1 = ybuf + NMMA * 8 * kYStride;  // second k-half
         bool finish = (seg_kb0 == 0 && kb == nkb - 1);
         if (!finish) {
             const int which = (cb == first_cb) ? 0 : 1;
             float* slot = a.partials + ((size_t)(cta * 2 + which) * a.rows) * 128;
-            for (int i = tid; i < a.rows * 128; i += kConsumerThreads)
-                slot[i] = ybuf[(i >> 7) * kYStride + (i & 127)];
+            for (int i = tid; i < a.rows * 128; i += kConsumerThreads) {
+                const int o = (i >> 7) * kYStride + (i & 127);
+                slot[i] = ybuf[o] + y1[o];
+            }
             __threadfence();
             named_bar_sync(1, kConsumerThreads);
             const int c_first = item_owner(n_items, (int64_t)cb * nkb, grid);
@@ -238,13 +309,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvArgs a)
             }
         }
         if (finish) {
+            const bool direct = (seg_kb0 == 0 && kb == nkb - 1);  // both k-halves still apart
             const int sv_off = a.blocks ? a.blocks[cb].sv_off : cb * 128;
             const int y_off = a.blocks ? a.blocks[cb].y_off : cb * 128;
             for (int n = warp; n < a.rows; n += kConsumerWarps) {
                 float v[4];
 #pragma unroll
-                for (int q = 0; q < 4; q++)
-                    v[q] = __half2float(__float2half_rn(ybuf[n * kYStride + 4 * lane + q]));
+                for (int q = 0; q < 4; q++) {
+                    const int o = n * kYStride + 4 * lane + q;
+                    const float f = direct ? ybuf[o] + y1[o] : ybuf[o];
+                    v[q] = __half2float(__float2half_rn(f));
+                }
                 if (!a.raw_out) {
                     had128_warp(v, lane);
 #pragma unroll
@@ -285,26 +360,45 @@ void gemv_set_tuning(int ctas_per_sm, int smem_budget_bytes)
         g_smem_budget = smem_budget_bytes;
 }
 
-template <int K, int CB, int NMMA>
+template <int K, int CB, int NMMA, bool FAST>
 static int launch_gemv_t(GemvArgs a, bool pdl, cudaStream_t s)
 {
     using L = GemvLayout<K, NMMA>;
     int budget = g_smem_budget;
     if (g_ctas_per_sm == 1) budget = std::max(budget, 200 * 1024);
-    int stages = (budget - L::kStage0) / L::kStageBytes;
+    const int stage_bytes = x_stage_bytes(a.rows) + L::kWeightBytes;
+    int stages = (budget - L::kStage0) / stage_bytes;
     stages = std::min(stages, kMaxStages);
     if (stages < 2) return EXL3_E_UNSUPPORTED;
     a.stages = stages;
-    const size_t smem = (size_t)L::kStage0 + (size_t)stages * L::kStageBytes;
+    const size_t smem = (size_t)L::kStage0 + (size_t)stages * stage_bytes;
 
     static bool attr_set[16] = {};  // per device
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 16 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<K, CB, NMMA>,
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<K, CB, NMMA, FAST>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
         if (e != cudaSuccess) return note_cuda(e);
         attr_set[dev] = true;
+    }
+    CUtensorMap tm_w, tm_x;
+    {
+        const uint64_t dims[3] = {(uint64_t)L::kTileWords, (uint64_t)a.t_out_total, (uint64_t)a.t_in};
+        const uint64_t strides[2] = {(uint64_t)L::kTileWords * 4,
+                                     (uint64_t)a.t_out_total * L::kTileWords * 4};
+        const uint32_t box[3] = {(uint32_t)L::kTileWords, 8u, 8u};
+        int rc = make_tensor_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, a.trellis, dims, strides,
+                                 box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+        // xh viewed as (32 words, rows, in/32): one box brings the four quarters of a k-block
+        const uint64_t in = (uint64_t)a.t_in * 16;
+        const uint64_t xdims[3] = {32u, (uint64_t)a.x_rows_total, in / 32};
+        const uint64_t xstrides[2] = {in * 4, 128u};
+        const uint32_t xbox[3] = {32u, (uint32_t)a.rows, 4u};
+        rc = make_tensor_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, a.xh, xdims, xstrides, xbox,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
     }
     const int64_t n_items = (int64_t)a.ncb * (a.t_in >> 3);
     int64_t grid = (int64_t)device_sm_count() * g_ctas_per_sm;
@@ -320,19 +414,26 @@ static int launch_gemv_t(GemvArgs a, bool pdl, cudaStream_t s)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return note_cuda(cudaLaunchKernelEx(&cfg, gemv_kernel<K, CB, NMMA>, a));
+    return note_cuda(cudaLaunchKernelEx(&cfg, gemv_kernel<K, CB, NMMA, FAST>, a, tm_w, tm_x));
+}
+
+template <int K, int CB> static int launch_gemv_kc(const GemvArgs& a, bool pdl, cudaStream_t s)
+{
+    const bool two = a.rows > 8;
+    // MUL1 has no two-halves form: its fast mode is the exact one
+    const bool fast = a.fast_accum && CB != CB_MUL1;
+    if (fast)
+        return two ? launch_gemv_t<K, CB, 2, (CB != CB_MUL1)>(a, pdl, s)
+                   : launch_gemv_t<K, CB, 1, (CB != CB_MUL1)>(a, pdl, s);
+    return two ? launch_gemv_t<K, CB, 2, false>(a, pdl, s) : launch_gemv_t<K, CB, 1, false>(a, pdl, s);
 }
 
 template <int K> static int launch_gemv_k(const GemvArgs& a, int cb, bool pdl, cudaStream_t s)
 {
-    const bool two = a.rows > 8;
     switch (cb) {
-        case CB_3INST:
-            return two ? launch_gemv_t<K, CB_3INST, 2>(a, pdl, s) : launch_gemv_t<K, CB_3INST, 1>(a, pdl, s);
-        case CB_MCG:
-            return two ? launch_gemv_t<K, CB_MCG, 2>(a, pdl, s) : launch_gemv_t<K, CB_MCG, 1>(a, pdl, s);
-        case CB_MUL1:
-            return two ? launch_gemv_t<K, CB_MUL1, 2>(a, pdl, s) : launch_gemv_t<K, CB_MUL1, 1>(a, pdl, s);
+        case CB_3INST: return launch_gemv_kc<K, CB_3INST>(a, pdl, s);
+        case CB_MCG: return launch_gemv_kc<K, CB_MCG>(a, pdl, s);
+        case CB_MUL1: return launch_gemv_kc<K, CB_MUL1>(a, pdl, s);
         default: return EXL3_E_CODEBOOK;
     }
 }

@@ -34,9 +34,13 @@ int launch_unpack(const uint32_t* trellis, int64_t n_tiles, int k, uint16_t* out
 int launch_decode(const uint32_t* trellis, int64_t t_in, int64_t t_out, int k, int cb, int64_t tn0,
                   int64_t tn_count, __half* w, int64_t ld, cudaStream_t s);
 int launch_table(int cb, __half* table, cudaStream_t s);
+// Output forms of the rotation kernel: plain fp16, or one 32-bit word per element holding
+// (x, 0) / (x, x) for the GEMV's two-slot activation fragments.
+enum : int { HAD_OUT_F16 = 0, HAD_OUT_PAIR_X0 = 1, HAD_OUT_PAIR_XX = 2 };
 int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
                     const __half* pre, const __half* post, __half* out, const int32_t* row_src,
-                    const int32_t* pre_row, const int32_t* post_row, bool pdl, cudaStream_t s);
+                    const int32_t* pre_row, const int32_t* post_row, bool pdl, int out_mode,
+                    cudaStream_t s);
 
 // One logical 128-column output block of a streamed GEMV: where its weights, activations,
 // output scales and results live.  NULL descriptor table = the identity mapping of a plain
@@ -50,7 +54,7 @@ struct ColBlock {
 
 struct GemvArgs {
     const uint32_t* trellis;   // (t_in, t_out_total, 8K) words
-    const __half* xh;          // rotated activations, rows of `in` halves
+    const uint32_t* xh;        // rotated activations, one 32-bit word per element (see HAD_OUT_*)
     const __half* svh;         // may be NULL
     const __half* bias;        // may be NULL
     __half* y;
@@ -63,8 +67,10 @@ struct GemvArgs {
     int t_out_total;           // tile columns of the trellis tensor
     int ncb;                   // logical 128-column blocks to compute
     int rows;                  // activation rows per block (1..16)
+    int x_rows_total;          // rows of the xh matrix (>= xrow + rows of every block)
     int stages;                // depth of the shared-memory ring
     int raw_out;               // 1: write fp16(y_inner) without rotation (MoE gate/up)
+    int fast_accum;            // 1: xh holds (x, x) and the MMA adds the codebook halves
 };
 
 int launch_gemv(const GemvArgs& a, int k, int cb, bool pdl, cudaStream_t s);

@@ -52,6 +52,7 @@ class EXL3Linear(torch.nn.Module):
         self._svh = None if svh is None else _to_dev_u16(svh.astype(np.float16), device)
         self._bias = None if layer.bias is None else _to_dev_u16(layer.bias.astype(np.float16), device)
         self.pdl = False
+        self.fast_accum = False
 
     def extra_repr(self) -> str:
         return f"in={self.in_features}, out={self.out_features}, k={self.k}, cb={self.cb}"
@@ -72,11 +73,11 @@ class EXL3Linear(torch.nn.Module):
                                device=x.device)
         if rows <= GEMV_MAX_ROWS:
             y = ops.gemv(x2d, self._trellis, self.k, self.cb, self._suh, self._svh, self._bias,
-                         pdl=self.pdl)
+                         pdl=self.pdl, fast_accum=self.fast_accum)
         else:
             y = torch.empty((rows, self.out_features), dtype=torch.float16, device=x.device)
             for r0 in range(0, rows, GEMV_MAX_ROWS):
                 r1 = min(rows, r0 + GEMV_MAX_ROWS)
                 ops.gemv(x2d[r0:r1], self._trellis, self.k, self.cb, self._suh, self._svh,
-                         self._bias, pdl=self.pdl, out=y[r0:r1])
+                         self._bias, pdl=self.pdl, fast_accum=self.fast_accum, out=y[r0:r1])
         return y.reshape(in_shape[:-1] + (self.out_features,))

@@ -80,6 +80,8 @@ def unpack_trellis(packed: torch.Tensor, k: int) -> torch.Tensor:
     packed = as_u16(packed).contiguous()
     out = torch.empty(packed.shape[:2] + (256,), dtype=torch.int16, device=packed.device)
     n = packed.shape[0] * packed.shape[1]
+    if n == 0:
+        return out
     _lib.check(_lib.load().exl3_unpack(packed.data_ptr(), n, k, out.data_ptr(),
                                        _stream(packed.device)), "exl3_unpack")
     return out
@@ -104,6 +106,8 @@ def decode_packed_trellis(trellis: torch.Tensor, k: int, cb: int, *, n_offset: i
         raise ValueError("slice exceeds output features")
     trellis = as_u16(trellis).contiguous()
     w = torch.empty((t_in * 16, n_count), dtype=torch.float16, device=trellis.device)
+    if w.numel() == 0:
+        return w
     _lib.check(_lib.load().exl3_decode(trellis.data_ptr(), t_in, t_out, k, int(cb), n_offset // 16,
                                        n_count // 16, w.data_ptr(), n_count,
                                        _stream(trellis.device)), "exl3_decode")
@@ -144,7 +148,7 @@ def had_r_128(x: torch.Tensor, *, pre_scale: torch.Tensor | None = None,
 
 def gemv(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh: torch.Tensor | None,
          svh: torch.Tensor | None, bias: torch.Tensor | None, *, pdl: bool = False,
-         out: torch.Tensor | None = None) -> torch.Tensor:
+         fast_accum: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
     """The whole linear forward for 1..16 rows in two launches (rotation, streamed GEMV).
     x2d (rows, in) fp16/bf16/fp32 -> (rows, out) fp16."""
     _need_cuda(x2d, "x")
@@ -163,6 +167,7 @@ def gemv(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh: torch.T
         x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out,
         k, int(cb), None if suh is None else suh.data_ptr(),
         None if svh is None else svh.data_ptr(), None if bias is None else bias.data_ptr(),
-        y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes, _lib.FLAG_PDL if pdl else 0,
+        y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes,
+        (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0),
         _stream(x2d.device)), "exl3_gemv")
     return y

@@ -35,6 +35,16 @@ extern "C" int emul_unpack_tile(const uint32_t* words, int k, uint16_t* cw256)
     return 0;
 }
 
+// K = 4 fast path: lane t reads word t and word (t - 1) mod 32 of the tile.
+extern "C" void emul_unpack_tile_k4_fast(const uint32_t* words, uint16_t* cw256)
+{
+    for (int lane = 0; lane < 32; lane++) {
+        uint32_t cw[8];
+        exl3::lane_codewords_k4(words[lane], words[(lane + 31) & 31], cw);
+        for (int j = 0; j < 8; j++) cw256[lane * 8 + j] = (uint16_t)cw[j];
+    }
+}
+
 extern "C" uint32_t emul_codebook_word(int cb, uint32_t cw)
 {
     if (cb == 0) return exl3::codebook_word<exl3::CB_3INST>(cw);

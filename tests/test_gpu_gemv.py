@@ -146,6 +146,21 @@ def test_dtypes_shapes_and_no_parameters(mod, oracle):
     assert rel_err(y2, oracle.linear_forward(x1, layer.trellis, 4, 0, None, None)) <= REL_TOL
 
 
+@pytest.mark.parametrize("k", [2, 4, 5, 8])
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("rows", [1, 11])
+def test_fast_accum_mode_stays_within_tolerance(mod, oracle, k, cb, rows):
+    """EXL3_FLAG_FAST_ACCUM adds the two fp16 halves of a codebook value inside the fp32
+    accumulation instead of rounding their sum first: same 1e-3 bound."""
+    layer = _layer(mod, k, 2048, 512, seed=300 + k + cb, cb=cb)
+    m = mod.EXL3Linear(layer)
+    m.fast_accum = True
+    x = np.random.default_rng(rows).standard_normal((rows, 2048)).astype(np.float16)
+    y = m(torch.from_numpy(x).cuda()).cpu().numpy()
+    want = oracle.linear_forward(x, layer.trellis, k, cb, layer.suh, layer.svh, None)
+    assert rel_err(y, want) <= REL_TOL
+
+
 def test_more_than_16_rows(mod, oracle):
     layer = _layer(mod, 3, 384, 256, seed=4)
     x = np.random.default_rng(2).standard_normal((37, 384)).astype(np.float16)

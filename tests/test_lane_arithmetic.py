@@ -44,6 +44,19 @@ def test_lane_windows_match_oracle(emul, oracle, k):
         np.testing.assert_array_equal(got, oracle.unpack_trellis_tile(packed, k))
 
 
+def test_k4_fast_path_matches_oracle(emul, oracle):
+    emul.emul_unpack_tile_k4_fast.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    rng = np.random.default_rng(44)
+    tiles = rng.integers(0, 65536, size=(200, 64), dtype=np.uint16)
+    tiles[0] = 0xFFFF
+    tiles[1] = 0
+    tiles[1, 0] = 0x8001
+    for packed in tiles:
+        got = np.empty(256, dtype=np.uint16)
+        emul.emul_unpack_tile_k4_fast(packed.ctypes.data, got.ctypes.data)
+        np.testing.assert_array_equal(got, oracle.unpack_trellis_tile(packed, 4))
+
+
 @pytest.mark.parametrize("cb", [0, 1, 2])
 def test_codebook_integer_half(emul, oracle, cb):
     table = oracle.codebook_table(cb)
