@@ -254,6 +254,9 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     a.x_rows_total = rows;
     a.raw_out = 0;
     a.fast_accum = fast ? 1 : 0;
+#ifdef EXL3_PROFILE
+    a.prof = reinterpret_cast<long long*>(ws + ((need + 255) & ~(size_t)255));  // behind xh: timing runs only
+#endif
     return launch_gemv(a, k, cb, pdl, s);
 }
 

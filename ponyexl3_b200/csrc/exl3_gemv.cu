@@ -14,8 +14,10 @@
 // of the first ring fill are issued BEFORE the programmatic-launch wait, so under
 // EXL3_FLAG_PDL a layer's weights stream while the previous kernel drains.
 //
-// Eight consumer warps; warp w owns tile columns 2*(w&3), 2*(w&3)+1 of the block and
-// the k-half (w>>2) of the item, so one activation fragment load serves two tiles.
+// Sixteen consumer warps (the decode chains need ~32 resident warps per SM to hide
+// their latency; two CTAs per SM give that); warp w owns tile columns 2*(w&3),
+// 2*(w&3)+1 of the block and the k-quarter (w>>2) of the item, so one activation
+// fragment load serves two tiles.
 // The decode is bound by the half-rate logic pipe of the SM (64 lanes/clk: LOP3, PRMT;
 // shifts run at a quarter), so the inner loop is written to spend exactly two logic
 // operations per weight at K = 4 — one byte-permute to cut the codeword window, one
@@ -40,7 +42,9 @@
 
 namespace exl3 {
 
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 16;
+constexpr int kKGroups = kConsumerWarps / 4;        // warps that split the item's 8 tile rows
+constexpr int kTileRowsPerWarp = 8 / kKGroups;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kGemvThreads = kConsumerThreads + 32;
 constexpr int kYStride = 132;
@@ -50,7 +54,7 @@ constexpr int kHeaderBytes = 512;
 template <int K, int NMMA> struct GemvLayout {
     static constexpr int kTileWords = 8 * K;
     static constexpr int kWeightBytes = 64 * kTileWords * 4;      // 8x8 tiles: 2048 * K
-    static constexpr int kYBytes = 2 * NMMA * 8 * kYStride * 4;   // one copy per k-half
+    static constexpr int kYBytes = kKGroups * NMMA * 8 * kYStride * 4;   // one copy per k-group
     static constexpr int kStage0 = (kHeaderBytes + kYBytes + 1023) / 1024 * 1024;
 };
 
@@ -122,21 +126,22 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         const uint32_t tx = L::kWeightBytes + (uint32_t)a.rows * 512u;
         tma_prefetch_desc(&tm_w);
         tma_prefetch_desc(&tm_x);
-        auto issue_weights = [&](int li) {
-            const int64_t it = it_begin + li;
-            const int cb = (int)(it / nkb), kb = (int)(it % nkb);
-            const int phys = a.blocks ? a.blocks[cb].phys : cb;
-            const int s = li % ns;
+        // (cb, kb) of the next item to fetch, advanced without divisions: the producer is one
+        // lane sharing its scheduler with busy consumer warps, so its per-item instruction
+        // chain must stay short or it becomes the bottleneck of the whole CTA.
+        int w_cb = (int)(it_begin / nkb), w_kb = (int)(it_begin % nkb);
+        int x_cb = w_cb, x_kb = w_kb;
+        auto issue_weights = [&](int s) {
+            const int phys = a.blocks ? a.blocks[w_cb].phys : w_cb;
             tma_load_3d(smem_u32(stage0 + (size_t)s * stage_bytes + xbytes), &tm_w, 0, 8 * phys,
-                        8 * kb, smem_u32(&full[s]));
+                        8 * w_kb, smem_u32(&full[s]));
+            if (++w_kb == nkb) { w_kb = 0; ++w_cb; }
         };
-        auto issue_x = [&](int li) {
-            const int64_t it = it_begin + li;
-            const int cb = (int)(it / nkb), kb = (int)(it % nkb);
-            const int xrow = a.blocks ? a.blocks[cb].xrow : 0;
-            const int s = li % ns;
-            tma_load_3d(smem_u32(stage0 + (size_t)s * stage_bytes), &tm_x, 0, xrow, 4 * kb,
+        auto issue_x = [&](int s) {
+            const int xrow = a.blocks ? a.blocks[x_cb].xrow : 0;
+            tma_load_3d(smem_u32(stage0 + (size_t)s * stage_bytes), &tm_x, 0, xrow, 4 * x_kb,
                         smem_u32(&full[s]));
+            if (++x_kb == nkb) { x_kb = 0; ++x_cb; }
         };
         // A block table is written by an earlier kernel of the stream: read it only
         // after the dependency wait.  Plain layers prefetch their weights first.
@@ -148,15 +153,30 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         }
         if (!a.blocks) griddep_wait();
         for (int li = 0; li < pre; li++) issue_x(li);
+        int s = 0;
+        uint32_t parity = 0;
+#ifdef EXL3_PROFILE
+        long long pprof_wait = 0, pprof_start = clock64();
+#endif
         for (int li = pre; li < nitems; li++) {
-            const int s = li % ns;
-            if (!mbar_wait(smem_u32(&empty[s]), (uint32_t)((li / ns) - 1) & 1u)) {
+#ifdef EXL3_PROFILE
+            long long tq0 = clock64();
+#endif
+            if (!mbar_wait(smem_u32(&empty[s]), parity)) {
                 atomicOr(a.status, ST_WAIT_EMPTY_TIMEOUT);
                 return;  // consumers run into their own bounded waits and finish
             }
+#ifdef EXL3_PROFILE
+            pprof_wait += clock64() - tq0;
+            if (li == nitems - 1 && a.prof) {
+                a.prof[(cta * 17 + 16) * 4 + 0] = pprof_wait;
+                a.prof[(cta * 17 + 16) * 4 + 2] = clock64() - pprof_start;
+            }
+#endif
             mbar_arrive_expect_tx(smem_u32(&full[s]), tx);
-            issue_weights(li);
-            issue_x(li);
+            issue_weights(s);
+            issue_x(s);
+            if (++s == ns) { s = 0; parity ^= 1u; }
         }
         return;
     }
@@ -169,52 +189,61 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
     LaneWords<K> lw;
     lw.init(lane);
     const int g = lane >> 2, tig = lane & 3;
-    const int tnp = warp & 3, kh = warp >> 2;
+    const int tnp = warp & 3, kg = warp >> 2;
     const int prev_word = (lane + 31) & 31;
 
-    // Byte offsets of this lane's activation words for the four tile rows of its k-half:
+    // Byte offsets of this lane's activation words for the tile rows of its k-group:
     // element e = 16*tk + 2*tig (+8 for the second MMA) of the 128-value block sits in
     // quarter e/32, line `row`, chunk ((e%32)/4) ^ (line & 7), byte 8*(tig&1).
-    int xoff[4][2];
+    int xoff[kTileRowsPerWarp][2];
 #pragma unroll
-    for (int tl = 0; tl < 4; tl++)
+    for (int tl = 0; tl < kTileRowsPerWarp; tl++)
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int tk = 4 * kh + tl;
+            const int tk = kTileRowsPerWarp * kg + tl;
             const int q = tk >> 1;
             const int chunk = 4 * (tk & 1) + (tig >> 1) + 2 * h;
             const int line = q * a.rows + g;  // rows of the second MMA group add 8 lines
             xoff[tl][h] = line * 128 + ((chunk ^ (line & 7)) << 4) + 8 * (tig & 1);
         }
 
-    float acc[2][NMMA][2][4];
+    float acc[2][NMMA][4];
 #pragma unroll
     for (int t = 0; t < 2; t++)
 #pragma unroll
         for (int m = 0; m < NMMA; m++)
 #pragma unroll
-            for (int h = 0; h < 2; h++)
-#pragma unroll
-                for (int q = 0; q < 4; q++) acc[t][m][h][q] = 0.f;
+            for (int q = 0; q < 4; q++) acc[t][m][q] = 0.f;
 
+#ifdef EXL3_PROFILE
+    long long prof_wait = 0, prof_comp = 0, prof_start = clock64();
+#endif
     bool failed = false;
     const int first_cb = (int)(it_begin / nkb);
     int seg_kb0 = (int)(it_begin % nkb);
 
+    int cb = first_cb, kb = seg_kb0 - 1, s = -1;
+    uint32_t parity = 0;
     for (int li = 0; li < nitems; li++) {
-        const int64_t it = it_begin + li;
-        const int cb = (int)(it / nkb), kb = (int)(it % nkb);
-        const int s = li % ns;
-        if (!failed && !mbar_wait(smem_u32(&full[s]), (uint32_t)(li / ns) & 1u)) {
+        if (++kb == nkb) { kb = 0; ++cb; }
+        if (++s == ns) { s = 0; parity ^= 1u; }
+#ifdef EXL3_PROFILE
+        long long tp0 = clock64();
+#endif
+        if (!failed && !mbar_wait(smem_u32(&full[s]), parity)) {
             failed = true;
             if (lane == 0) atomicOr(a.status, ST_WAIT_FULL_TIMEOUT);
         }
+#ifdef EXL3_PROFILE
+        long long tp1 = clock64();
+        prof_wait += tp1 - tp0;
+#endif
         if (!failed) {
             const uint8_t* xst = stage0 + (size_t)s * stage_bytes;
             const uint32_t* wst = reinterpret_cast<const uint32_t*>(xst + xbytes) +
-                                  (4 * kh * 8 + 2 * tnp) * L::kTileWords;
+                                  (kTileRowsPerWarp * kg * 8 + 2 * tnp) * L::kTileWords;
 #pragma unroll
-            for (int tl = 0; tl < 4; tl++) {
+            for (int tl = 0; tl < kTileRowsPerWarp; tl++) {
                 // activation fragments: rows g (+8), k-slots of this lane
                 uint2 xb[NMMA][2];
 #pragma unroll
@@ -247,42 +276,56 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
                     const uint32_t a2[4] = {d[2], d[6], d[3], d[7]};
 #pragma unroll
                     for (int m = 0; m < NMMA; m++) {
-                        mma_16816(acc[t][m][0], a1, xb[m][0].x, xb[m][0].y);
-                        mma_16816(acc[t][m][1], a2, xb[m][1].x, xb[m][1].y);
+                        mma_16816(acc[t][m], a1, xb[m][0].x, xb[m][0].y);
+                        mma_16816(acc[t][m], a2, xb[m][1].x, xb[m][1].y);
                     }
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&empty[s]));
+#ifdef EXL3_PROFILE
+        long long tp2 = clock64();
+        prof_comp += tp2 - tp1;
+        if (li == nitems - 1 && lane == 0 && a.prof) {
+            a.prof[(cta * 17 + warp) * 4 + 0] = prof_wait;
+            a.prof[(cta * 17 + warp) * 4 + 1] = prof_comp;
+            a.prof[(cta * 17 + warp) * 4 + 2] = tp2 - prof_start;
+            a.prof[(cta * 17 + warp) * 4 + 3] = nitems;
+        }
+#endif
 
         if (kb != nkb - 1 && li != nitems - 1) continue;
 
         // ---- end of this CTA's share of column block cb -------------------------------
-        float* yk = ybuf + kh * (NMMA * 8 * kYStride);
+        constexpr int kYCopy = NMMA * 8 * kYStride;  // floats per k-group copy
+        float* yk = ybuf + kg * kYCopy;
 #pragma unroll
         for (int t = 0; t < 2; t++)
 #pragma unroll
             for (int m = 0; m < NMMA; m++) {
                 float* y0 = yk + (2 * tig + 8 * m) * kYStride + 16 * (2 * tnp + t) + g;
-                y0[0] = acc[t][m][0][0] + acc[t][m][1][0];
-                y0[kYStride] = acc[t][m][0][1] + acc[t][m][1][1];
-                y0[8] = acc[t][m][0][2] + acc[t][m][1][2];
-                y0[kYStride + 8] = acc[t][m][0][3] + acc[t][m][1][3];
+                y0[0] = acc[t][m][0];
+                y0[kYStride] = acc[t][m][1];
+                y0[8] = acc[t][m][2];
+                y0[kYStride + 8] = acc[t][m][3];
 #pragma unroll
-                for (int h = 0; h < 2; h++)
-#pragma unroll
-                    for (int q = 0; q < 4; q++) acc[t][m][h][q] = 0.f;
+                for (int q = 0; q < 4; q++) acc[t][m][q] = 0.f;
             }
         named_bar_sync(1, kConsumerThreads);
-        const float* y1 = ybuf + NMMA * 8 * kYStride;  // second k-half
+        auto ysum = [&](int o) {  // the k-groups' copies, added in a fixed order
+            float f = ybuf[o];
+#pragma unroll
+            for (int c = 1; c < kKGroups; c++) f += ybuf[o + c * kYCopy];
+            return f;
+        };
         bool finish = (seg_kb0 == 0 && kb == nkb - 1);
         if (!finish) {
             const int which = (cb == first_cb) ? 0 : 1;
             float* slot = a.partials + ((size_t)(cta * 2 + which) * a.rows) * 128;
             for (int i = tid; i < a.rows * 128; i += kConsumerThreads) {
                 const int o = (i >> 7) * kYStride + (i & 127);
-                slot[i] = ybuf[o] + y1[o];
+                slot[i] = ysum(o);
             }
             __threadfence();
             named_bar_sync(1, kConsumerThreads);
@@ -309,7 +352,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             }
         }
         if (finish) {
-            const bool direct = (seg_kb0 == 0 && kb == nkb - 1);  // both k-halves still apart
+            const bool direct = (seg_kb0 == 0 && kb == nkb - 1);  // k-group copies still apart
             const int sv_off = a.blocks ? a.blocks[cb].sv_off : cb * 128;
             const int y_off = a.blocks ? a.blocks[cb].y_off : cb * 128;
             for (int n = warp; n < a.rows; n += kConsumerWarps) {
@@ -317,7 +360,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     const int o = n * kYStride + 4 * lane + q;
-                    const float f = direct ? ybuf[o] + y1[o] : ybuf[o];
+                    const float f = direct ? ysum(o) : ybuf[o];
                     v[q] = __half2float(__float2half_rn(f));
                 }
                 if (!a.raw_out) {

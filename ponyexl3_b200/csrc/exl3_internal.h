@@ -70,6 +70,7 @@ struct GemvArgs {
     int x_rows_total;          // rows of the xh matrix (>= xrow + rows of every block)
     int stages;                // depth of the shared-memory ring
     int raw_out;               // 1: write fp16(y_inner) without rotation (MoE gate/up)
+    long long* prof;           // EXL3_PROFILE builds only: per-warp cycle counters, else NULL
     int fast_accum;            // 1: xh holds (x, x) and the MMA adds the codebook halves
 };
 
