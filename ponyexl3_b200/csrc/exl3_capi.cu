@@ -231,10 +231,13 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     const bool fast = (flags & EXL3_FLAG_FAST_ACCUM) != 0 && cb != CB_MUL1;
     cudaStream_t s = (cudaStream_t)stream;
 
-    rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
-                         nullptr, reinterpret_cast<__half*>(xh), nullptr, nullptr, nullptr, pdl,
-                         fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s);
-    if (rc) return rc;
+    const bool x_fused = gemv_x_is_fused(rows, (int)t_in, (int)(t_out / 8));
+    if (!x_fused) {
+        rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
+                             nullptr, reinterpret_cast<__half*>(xh), nullptr, nullptr, nullptr, pdl,
+                             fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s);
+        if (rc) return rc;
+    }
 
     GemvArgs a = {};
     a.trellis = reinterpret_cast<const uint32_t*>(trellis);
@@ -254,9 +257,11 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     a.x_rows_total = rows;
     a.raw_out = 0;
     a.fast_accum = fast ? 1 : 0;
-#ifdef EXL3_PROFILE
-    a.prof = reinterpret_cast<long long*>(ws + ((need + 255) & ~(size_t)255));  // behind xh: timing runs only
-#endif
+    a.x = x;
+    a.suh = reinterpret_cast<const __half*>(suh);
+    a.x_row_stride = x_row_stride;
+    a.x_dtype = x_dtype;
+    a.x_fused = x_fused ? 1 : 0;
     return launch_gemv(a, k, cb, pdl, s);
 }
 

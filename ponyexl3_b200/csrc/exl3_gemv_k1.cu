@@ -1,0 +1,6 @@
+// Streamed GEMV kernels for K = 1 bits per weight (all codebooks, row groups and modes).
+#include "exl3_gemv.cuh"
+
+namespace exl3 {
+template int launch_gemv_k<1>(const GemvArgs&, int, bool, cudaStream_t);
+}

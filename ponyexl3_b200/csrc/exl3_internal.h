@@ -70,10 +70,19 @@ struct GemvArgs {
     int x_rows_total;          // rows of the xh matrix (>= xrow + rows of every block)
     int stages;                // depth of the shared-memory ring
     int raw_out;               // 1: write fp16(y_inner) without rotation (MoE gate/up)
-    long long* prof;           // EXL3_PROFILE builds only: per-warp cycle counters, else NULL
-    int fast_accum;            // 1: xh holds (x, x) and the MMA adds the codebook halves
+    int fast_accum;
+    // fused input rotation (few rows): the kernel reads x itself
+    const void* x;             // raw activations
+    const __half* suh;         // may be NULL
+    int64_t x_row_stride;
+    int x_dtype;
+    int x_fused;               // 1: rotate x in the kernel; 0: xh was written by the rotation kernel
+    // filled in by the launcher
+    int ksplit;                // CTAs per cluster = k-slices per column block
+    int stage0_off;            // byte offset of the ring inside dynamic shared memory            // 1: xh holds (x, x) and the MMA adds the codebook halves
 };
 
 int launch_gemv(const GemvArgs& a, int k, int cb, bool pdl, cudaStream_t s);
+bool gemv_x_is_fused(int rows, int t_in, int ncb);
 
 }  // namespace exl3
