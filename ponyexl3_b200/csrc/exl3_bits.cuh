@@ -142,6 +142,17 @@ template <int CB> EXL3_HD uint32_t codebook_word(uint32_t cw)
     return (x & 0x8FFF8FFFu) ^ 0x3B603B60u;
 }
 
+// Same, with the XOR constant of 3INST / MCG (0x3B603B60) handed in as a run-time value.
+// The compiler will not keep a second 32-bit literal in a register and splits (x & m) ^ c
+// into two logic operations; a value it cannot see through stays in a register and the
+// pair becomes a single three-input LOP3 — one logic-pipe slot per weight saved.
+template <int CB> EXL3_HD uint32_t codebook_word_rt(uint32_t cw, uint32_t xor_const)
+{
+    if (CB == CB_MUL1) return codebook_word<CB>(cw);
+    uint32_t x = (CB == CB_3INST) ? cw * 89226354u + 64248484u : cw * 0xCBAC1FEDu;
+    return (x & 0x8FFF8FFFu) ^ xor_const;
+}
+
 // Tile position (row = input-feature offset, col = output-feature offset) of
 // codeword j of lane t (reference: ponyexl3/ref/perm.py:8-26).
 EXL3_HD int frag_row(int t, int j) { return (t & 3) * 2 + (j & 1) + ((j & 2) ? 8 : 0); }

@@ -113,9 +113,10 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr)
 }
 
 // (w, w) from the two-halves word of 3INST / MCG, or from the MUL1 pattern.
-template <int CB, bool FAST> __device__ __forceinline__ uint32_t weight_slot_pair(uint32_t cw)
+template <int CB, bool FAST>
+__device__ __forceinline__ uint32_t weight_slot_pair(uint32_t cw, uint32_t xor_const)
 {
-    const uint32_t r = codebook_word<CB>(cw);
+    const uint32_t r = codebook_word_rt<CB>(cw, xor_const);
     if (CB == CB_MUL1) {
         const __half2 h = u32_as_h2(r * 0x00010001u);
         return h2_as_u32(__hfma2(h, u32_as_h2(0x1EEE1EEEu), u32_as_h2(0xC931C931u)));
@@ -238,6 +239,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
     const int g = lane >> 2, tig = lane & 3;
     const int grp = warp >> 2, tnp = warp & 3;
     const int prev_word = (lane + 31) & 31;
+    const uint32_t xor_const = a.cb_xor;   // 0x3B603B60, kept opaque on purpose (see exl3_bits.cuh)
     LaneWords<K> lw;
     lw.init(lane);
 
@@ -344,7 +346,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
                         }
                         uint32_t d[8];
 #pragma unroll
-                        for (int j = 0; j < 8; j++) d[j] = weight_slot_pair<CB, FAST>(cw[j]);
+                        for (int j = 0; j < 8; j++) d[j] = weight_slot_pair<CB, FAST>(cw[j], xor_const);
                         // tile rows 2*tig, 2*tig+1 (codewords 0,4 | 1,5), then rows +8 (2,6 | 3,7)
                         const uint32_t a1[4] = {d[0], d[4], d[1], d[5]};
                         const uint32_t a2[4] = {d[2], d[6], d[3], d[7]};
@@ -470,6 +472,7 @@ static int launch_gemv_t(GemvArgs a, bool pdl, cudaStream_t s)
     int ksplit, grid;
     gemv_choose_split(a.ncb, nkb, &ksplit, &grid);
     a.ksplit = ksplit;
+    a.cb_xor = 0x3B603B60u;
     const int klen_max = (nkb + ksplit - 1) / ksplit;
     const int xs_bytes = XFUSED ? (klen_max * a.rows + 1) * kXsRowBytes : 0;
     const int stage0 = (kHeaderBytes + L::kYBytes + xs_bytes + 1023) / 1024 * 1024;
