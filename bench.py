@@ -302,10 +302,9 @@ def run_gpu(args):
     # ---- end to end through the module API with host buffers --------------------------------
     mods = []
     for L in layers:
-        m = EXL3Linear.__new__(EXL3Linear)
-        torch.nn.Module.__init__(m)
-        m.key, m.in_features, m.out_features, m.k, m.cb = "bench", L.inf, L.c1 - L.c0, K_BITS, CB
-        m._trellis, m._suh, m._svh, m._bias, m.pdl = L.trellis, L.suh, L.svh, None, True
+        m = EXL3Linear.from_device_tensors(trellis=L.trellis, k=K_BITS, cb=CB, suh=L.suh, svh=L.svh,
+                                           key="bench")
+        m.pdl = True
         mods.append(m)
     h_in = {inf: torch.randn((ROWS, inf)).to(torch.float16).pin_memory() for inf in xs}
     d_in = {inf: torch.empty_like(xs[inf]) for inf in xs}

@@ -109,11 +109,13 @@ EXL3_HD void mad_wide(uint32_t a, uint32_t b, uint32_t c_hi, uint32_t& lo, uint3
 // byte-aligned in V, even j in V << 4 (one wide multiply); every window is then one byte
 // permute with zero fill, and the top one falls out of the wide multiply for free:
 // 9 logic-pipe operations for 8 codewords instead of 16 shifts and masks.
-EXL3_HD void lane_codewords_k4(uint32_t w, uint32_t prev, uint32_t (&cw)[8])
+// `sixteen` is the number 16 handed in as a run-time value: a literal would be turned back
+// into shifts, which run on the quarter-rate shift unit instead of the multiplier.
+EXL3_HD void lane_codewords_k4(uint32_t w, uint32_t prev, uint32_t (&cw)[8], uint32_t sixteen = 16u)
 {
     const uint32_t p = prev & 0xFFFu;
     uint32_t lo4, hi4;
-    mad_wide(w, 16u, p * 16u, lo4, hi4);       // (hi4 : lo4) = V << 4, hi4 < 2^16
+    mad_wide(w, sixteen, p * sixteen, lo4, hi4);   // (hi4 : lo4) = V << 4, hi4 < 2^16
     cw[7] = byte_perm(w, 0u, 0x4410);
     cw[5] = byte_perm(w, 0u, 0x4421);
     cw[3] = byte_perm(w, 0u, 0x4432);

@@ -262,6 +262,9 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     a.x_row_stride = x_row_stride;
     a.x_dtype = x_dtype;
     a.x_fused = x_fused ? 1 : 0;
+#ifdef EXL3_PROFILE
+    a.prof = reinterpret_cast<long long*>(ws + kWsPartials);   // timing builds reuse the scratch area
+#endif
     return launch_gemv(a, k, cb, pdl, s);
 }
 

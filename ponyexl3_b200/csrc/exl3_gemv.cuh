@@ -234,11 +234,15 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
     }
 
     // ----------------------------------------------------------------- consumers ----
+#ifdef EXL3_PROFILE
+    long long pt_start = clock64(), pt_wait = 0, pt_comp = 0, pt_flush = 0;
+#endif
     griddep_wait();   // x (and, for the leader, y) belong to earlier kernels until they end
 
     const int g = lane >> 2, tig = lane & 3;
     const int grp = warp >> 2, tnp = warp & 3;
     const int prev_word = (lane + 31) & 31;
+    const uint32_t sixteen = 16u;   // a literal: measured faster than keeping these shifts on the multiplier
     const uint32_t xor_const = a.cb_xor;   // 0x3B603B60, kept opaque on purpose (see exl3_bits.cuh)
     LaneWords<K> lw;
     lw.init(lane);
@@ -297,6 +301,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         for (int m = 0; m < NMMA; m++)
 #pragma unroll
             for (int q = 0; q < 4; q++) acc[t][m][q] = 0.f;
+#ifdef EXL3_PROFILE
+    long long pt_pro = clock64();
+#endif
 
     bool failed = false;
     int li = grp;                         // this group's next item
@@ -309,10 +316,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         const int cb = cluster_id + cbi * n_clusters;
         const int li_end = (cbi + 1) * klen;
         for (; li < li_end; li += kGroups) {
+#ifdef EXL3_PROFILE
+            long long q0 = clock64();
+#endif
             if (!failed && !mbar_wait(smem_u32(&full[s]), parity)) {
                 failed = true;
                 if (lane == 0) atomicOr(a.status, ST_WAIT_FULL_TIMEOUT);
             }
+#ifdef EXL3_PROFILE
+            long long q1 = clock64();
+            pt_wait += q1 - q0;
+#endif
             if (!failed) {
                 const uint8_t* st = stage0 + (size_t)s * stage_bytes;
                 const uint32_t* wst =
@@ -338,7 +352,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
                         const uint32_t* tw = wst + (tk * 8 + t) * L::kTileWords;
                         uint32_t cw[8];
                         if (K == 4) {
-                            lane_codewords_k4(tw[lane], tw[prev_word], cw);
+                            lane_codewords_k4(tw[lane], tw[prev_word], cw, sixteen);
                         } else {
                             const uint32_t wa = tw[lw.i0], wb = tw[lw.i1];
                             const uint32_t wc = LaneWords<K>::kThree ? tw[lw.i2] : 0u;
@@ -362,7 +376,13 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             if (lane == 0) mbar_arrive(smem_u32(&empty[s]));
             s += kGroups;
             if (s >= ns) { s -= ns; parity ^= 1u; }
+#ifdef EXL3_PROFILE
+            pt_comp += clock64() - q1;
+#endif
         }
+#ifdef EXL3_PROFILE
+        long long f0 = clock64();
+#endif
 
         // ---- block cb is done in this CTA: gather the partial sums ------------------------
         if (red_pending) {   // the previous block's sums must have been read by the leader
@@ -400,6 +420,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             if (tid == 0) mbar_arrive_remote(map_to_cta(smem_u32(red_full), 0));
             red_pending = true;
             red_parity ^= 1u;
+#ifdef EXL3_PROFILE
+            pt_flush += clock64() - f0;
+#endif
             continue;
         }
         if (S > 1) {
@@ -449,12 +472,31 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         named_bar_sync(1, kConsumerThreads);   // all reads of ybuf (local and remote) are done
         if (S > 1 && tid == 0)
             for (int r = 1; r < S; r++) mbar_arrive_remote(map_to_cta(smem_u32(red_done), (uint32_t)r));
+#ifdef EXL3_PROFILE
+        pt_flush += clock64() - f0;
+#endif
     }
+#ifdef EXL3_PROFILE
+    long long pt_main = clock64();
+#endif
     // A non-leader's shared memory must outlive the leader's last read of it.
     if (red_pending && !failed) {
         if (!mbar_wait_cluster(smem_u32(red_done), red_parity ^ 1u) && lane == 0)
             atomicOr(a.status, ST_WAIT_FULL_TIMEOUT);
     }
+#ifdef EXL3_PROFILE
+    if (a.prof && lane == 0) {
+        long long* p = a.prof + ((size_t)blockIdx.x * kConsumerWarps + warp) * 8;
+        p[0] = pt_pro - pt_start;      // dependency wait + activation prologue
+        p[1] = pt_wait;                // waiting for ring stages
+        p[2] = pt_comp;                // decode + MMA
+        p[3] = pt_flush;               // gather / epilogue
+        p[4] = clock64() - pt_main;    // final wait for the leader
+        p[5] = clock64() - pt_start;   // total
+        p[6] = rank;
+        p[7] = nitems;
+    }
+#endif
 }
 
 // ---- host side ----------------------------------------------------------------------------------
@@ -473,6 +515,7 @@ static int launch_gemv_t(GemvArgs a, bool pdl, cudaStream_t s)
     gemv_choose_split(a.ncb, nkb, &ksplit, &grid);
     a.ksplit = ksplit;
     a.cb_xor = 0x3B603B60u;
+    a.sixteen = 16u;
     const int klen_max = (nkb + ksplit - 1) / ksplit;
     const int xs_bytes = XFUSED ? (klen_max * a.rows + 1) * kXsRowBytes : 0;
     const int stage0 = (kHeaderBytes + L::kYBytes + xs_bytes + 1023) / 1024 * 1024;

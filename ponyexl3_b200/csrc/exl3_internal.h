@@ -78,6 +78,8 @@ struct GemvArgs {
     int x_dtype;
     int x_fused;               // 1: rotate x in the kernel; 0: xh was written by the rotation kernel
     // filled in by the launcher
+    long long* prof;           // EXL3_PROFILE builds: per-warp cycle counters; NULL otherwise
+    uint32_t sixteen;          // the number 16 as a run-time value (keeps shifts on the multiplier)
     uint32_t cb_xor;           // XOR constant of the 3INST / MCG codebooks, as a run-time value
     int ksplit;                // CTAs per cluster = k-slices per column block
     int stage0_off;            // byte offset of the ring inside dynamic shared memory            // 1: xh holds (x, x) and the MMA adds the codebook halves

@@ -54,6 +54,26 @@ class EXL3Linear(torch.nn.Module):
         self.pdl = False
         self.fast_accum = False
 
+    @classmethod
+    def from_device_tensors(cls, *, trellis: torch.Tensor, k: int, cb: int,
+                            suh: torch.Tensor | None = None, svh: torch.Tensor | None = None,
+                            bias: torch.Tensor | None = None, key: str = "") -> "EXL3Linear":
+        """Build the module around tensors that already live on the device (a shard of a
+        larger layer, or synthetic weights): trellis (in/16, out/16, 16k) int16, fp16 vectors."""
+        if trellis.ndim != 3 or trellis.shape[2] != 16 * k:
+            raise ValueError(f"trellis shape {tuple(trellis.shape)} does not fit K={k}")
+        if (trellis.shape[0] * 16) % 128 or (trellis.shape[1] * 16) % 128:
+            raise ValueError("in/out features must be multiples of 128")
+        m = cls.__new__(cls)
+        torch.nn.Module.__init__(m)
+        m.key = key
+        m.in_features, m.out_features = trellis.shape[0] * 16, trellis.shape[1] * 16
+        m.k, m.cb = int(k), int(cb)
+        m._trellis, m._suh, m._svh, m._bias = trellis.contiguous(), suh, svh, bias
+        m.pdl = False
+        m.fast_accum = False
+        return m
+
     def extra_repr(self) -> str:
         return f"in={self.in_features}, out={self.out_features}, k={self.k}, cb={self.cb}"
 
