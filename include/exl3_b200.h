@@ -121,6 +121,18 @@ EXL3_API int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_strid
               const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
               size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
 
+/* Same contract for any number of rows (prefill): the packed tiles are decoded to fp16 in
+ * shared memory and multiplied on the tensor cores (tcgen05.mma, fp32 accumulators in tensor
+ * memory) against TMA-staged rotated activations; W is never materialised in global memory.
+ * Replaces the rows > 16 branches of EXL3Linear.__call__, ponyexl3/mlx/exl3_linear.py:137-161
+ * (decode_full_mlx + matmul, ponyexl3/mlx/gemv_metal.py:630-774, and the striped path).
+ * The workspace holds the rotated activations: exl3_gemm_workspace_bytes(rows, in). */
+EXL3_API size_t exl3_gemm_workspace_bytes(int64_t rows, int64_t in);
+EXL3_API int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_stride, const uint16_t* trellis,
+              int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
+              const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
+              size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

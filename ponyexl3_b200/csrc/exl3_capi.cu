@@ -268,6 +268,54 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     return launch_gemv(a, k, cb, pdl, s);
 }
 
+size_t exl3_gemm_workspace_bytes(int64_t rows, int64_t in)
+{
+    if (rows < 1) rows = 1;
+    if (in < 128) in = 128;
+    return ((size_t)kWsPartials + (size_t)rows * (size_t)in * 2 + 255) & ~(size_t)255;
+}
+
+int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_stride, const uint16_t* trellis,
+              int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
+              const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
+              size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+{
+    (void)flags;
+    if (!x || !trellis || !y) return EXL3_E_NULL;
+    if (k < 1 || k > 8) return EXL3_E_K;
+    if (cb < 0 || cb > 2) return EXL3_E_CODEBOOK;
+    if (t_in <= 0 || t_out <= 0 || t_in % 8 || t_out % 8) return EXL3_E_SHAPE;
+    if (t_in > (1 << 24) || t_out > (1 << 24)) return EXL3_E_SHAPE;
+    if (rows < 1 || rows > (1 << 30)) return EXL3_E_ROWS;
+    const int64_t in = 16 * t_in, out = 16 * t_out;
+    if (x_row_stride < in || y_row_stride < out) return EXL3_E_SHAPE;
+    int rc = check_dtype_align(x, x_dtype, x_row_stride);
+    if (rc) return rc;
+    if (!aligned(trellis, 16) || !aligned(y, 16) || y_row_stride % 8) return EXL3_E_ALIGN;
+    if ((suh && !aligned(suh, 8)) || (svh && !aligned(svh, 16)) || (bias && !aligned(bias, 16)))
+        return EXL3_E_ALIGN;
+    if (!workspace) return EXL3_E_WORKSPACE;
+    if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
+    if (workspace_bytes < exl3_gemm_workspace_bytes(rows, in)) return EXL3_E_WORKSPACE;
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    __half* xh = reinterpret_cast<__half*>(ws + kWsPartials);
+    cudaStream_t s = (cudaStream_t)stream;
+    rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh), nullptr,
+                         xh, nullptr, nullptr, nullptr, false, HAD_OUT_F16, s);
+    if (rc) return rc;
+    GemmArgs a = {};
+    a.svh = reinterpret_cast<const __half*>(svh);
+    a.bias = reinterpret_cast<const __half*>(bias);
+    a.y = reinterpret_cast<__half*>(y);
+    a.status = reinterpret_cast<int*>(ws + kWsStatus);
+    a.y_row_stride = y_row_stride;
+    a.m = (int)rows;
+    a.t_in = (int)t_in;
+    a.t_out = (int)t_out;
+    return launch_gemm(a, k, cb, xh, reinterpret_cast<const uint32_t*>(trellis), s);
+}
+
 /* Tuning hook used by the benchmark sweeps: CTAs per SM (1 or 2) and the dynamic
  * shared-memory budget per CTA of the streamed GEMV.  Not part of the stable ABI. */
 EXL3_API void exl3_tune_gemv(int ctas_per_sm, int smem_budget_bytes)

@@ -88,4 +88,21 @@ struct GemvArgs {
 int launch_gemv(const GemvArgs& a, int k, int cb, bool pdl, cudaStream_t s);
 bool gemv_x_is_fused(int rows, int t_in, int ncb);
 
+// ---- prefill GEMM (exl3_gemm.cuh) ---------------------------------------------------------
+struct GemmArgs {
+    const __half* svh;        // may be NULL
+    const __half* bias;       // may be NULL
+    __half* y;
+    int* status;
+    int64_t y_row_stride;
+    int m;                    // rows (tokens)
+    int t_in, t_out;          // tiles
+    int tiles_m, tiles_n;
+    int stages;
+    uint32_t cb_xor;
+};
+
+int launch_gemm(const GemmArgs& a, int k, int cb, const __half* xh, const uint32_t* trellis,
+                cudaStream_t s);
+
 }  // namespace exl3

@@ -5,7 +5,7 @@ Same construction and call contract as the reference's ``EXL3Linear``
 ``x[..., in]`` (fp16 / bf16 / fp32), returns fp16 ``[..., out]`` with the leading
 shape preserved, optional fp16 bias, no autograd, and the packed trellis kept out
 of the parameter tree.  Routing by row count replaces the reference's ladder:
-rows <= 16 take the streamed GEMV; larger batches take the prefill GEMM.
+rows <= 16 take the streamed GEMV; larger batches take the tensor-core prefill GEMM.
 """
 
 from __future__ import annotations
@@ -95,9 +95,5 @@ class EXL3Linear(torch.nn.Module):
             y = ops.gemv(x2d, self._trellis, self.k, self.cb, self._suh, self._svh, self._bias,
                          pdl=self.pdl, fast_accum=self.fast_accum)
         else:
-            y = torch.empty((rows, self.out_features), dtype=torch.float16, device=x.device)
-            for r0 in range(0, rows, GEMV_MAX_ROWS):
-                r1 = min(rows, r0 + GEMV_MAX_ROWS)
-                ops.gemv(x2d[r0:r1], self._trellis, self.k, self.cb, self._suh, self._svh,
-                         self._bias, pdl=self.pdl, fast_accum=self.fast_accum, out=y[r0:r1])
+            y = ops.gemm(x2d, self._trellis, self.k, self.cb, self._suh, self._svh, self._bias)
         return y.reshape(in_shape[:-1] + (self.out_features,))

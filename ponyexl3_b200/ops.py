@@ -38,26 +38,30 @@ class Workspace:
 
     _per_device: dict[int, "Workspace"] = {}
 
-    def __init__(self, device: torch.device, max_rows: int, max_in: int):
+    def __init__(self, device: torch.device, nbytes: int):
         lib = _lib.load()
         self.device = device
-        self.max_rows, self.max_in = max_rows, max_in
-        self.nbytes = int(lib.exl3_workspace_bytes(max_rows, max_in))
+        self.nbytes = int(nbytes)
         self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
         _lib.check(lib.exl3_workspace_init(self.buf.data_ptr(), self.nbytes, _stream(device)),
                    "exl3_workspace_init")
 
     @classmethod
-    def get(cls, device: torch.device, rows: int, in_features: int) -> "Workspace":
+    def get_bytes(cls, device: torch.device, nbytes: int) -> "Workspace":
+        """The device's workspace, re-allocated (after a stream sync) when it is too small."""
         idx = device.index if device.index is not None else torch.cuda.current_device()
         ws = cls._per_device.get(idx)
-        if ws is None or ws.max_rows < rows or ws.max_in < in_features:
+        if ws is None or ws.nbytes < nbytes:
             if ws is not None:
                 torch.cuda.current_stream(device).synchronize()
-            ws = Workspace(torch.device("cuda", idx), max(rows, ws.max_rows if ws else 16),
-                           max(in_features, ws.max_in if ws else 32768))
+            floor = int(_lib.load().exl3_workspace_bytes(16, 32768))
+            ws = Workspace(torch.device("cuda", idx), max(int(nbytes), floor, ws.nbytes if ws else 0))
             cls._per_device[idx] = ws
         return ws
+
+    @classmethod
+    def get(cls, device: torch.device, rows: int, in_features: int) -> "Workspace":
+        return cls.get_bytes(device, int(_lib.load().exl3_workspace_bytes(rows, in_features)))
 
     def status(self) -> int:
         import ctypes
@@ -170,4 +174,30 @@ def gemv(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh: torch.T
         y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes,
         (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0),
         _stream(x2d.device)), "exl3_gemv")
+    return y
+
+
+def gemm(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh: torch.Tensor | None,
+         svh: torch.Tensor | None, bias: torch.Tensor | None, *,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """The linear forward for any number of rows on the tensor cores (prefill).
+    x2d (rows, in) fp16/bf16/fp32 -> (rows, out) fp16."""
+    _need_cuda(x2d, "x")
+    rows, in_features = x2d.shape
+    t_in, t_out, _ = trellis.shape
+    if in_features != t_in * 16:
+        raise ValueError(f"x has {in_features} features, layer expects {t_in * 16}")
+    if x2d.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {x2d.dtype}")
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    lib = _lib.load()
+    ws = Workspace.get_bytes(x2d.device, int(lib.exl3_gemm_workspace_bytes(rows, in_features)))
+    y = out if out is not None else torch.empty((rows, t_out * 16), dtype=torch.float16,
+                                                device=x2d.device)
+    _lib.check(lib.exl3_gemm(
+        x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out,
+        k, int(cb), None if suh is None else suh.data_ptr(),
+        None if svh is None else svh.data_ptr(), None if bias is None else bias.data_ptr(),
+        y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes, 0, _stream(x2d.device)), "exl3_gemm")
     return y

@@ -161,7 +161,7 @@ def test_fast_accum_mode_stays_within_tolerance(mod, oracle, k, cb, rows):
     assert rel_err(y, want) <= REL_TOL
 
 
-def test_more_than_16_rows(mod, oracle):
+def test_more_than_16_rows_go_to_the_gemm(mod, oracle):
     layer = _layer(mod, 3, 384, 256, seed=4)
     x = np.random.default_rng(2).standard_normal((37, 384)).astype(np.float16)
     _check(mod, oracle, layer, x)
