@@ -179,8 +179,7 @@ size_t exl3_workspace_bytes(int64_t max_rows, int64_t max_in)
 {
     if (max_rows < 1) max_rows = 1;
     if (max_in < 128) max_in = 128;
-    const int64_t rows_per_block = max_rows < 16 ? max_rows : 16;
-    size_t b = kWsPartials + ws_partial_bytes(rows_per_block);
+    size_t b = kWsScratch;
     b += (size_t)max_rows * (size_t)max_in * 4;  // rotated activations, one word per element
     return (b + 255) & ~(size_t)255;
 }
@@ -188,9 +187,9 @@ size_t exl3_workspace_bytes(int64_t max_rows, int64_t max_in)
 int exl3_workspace_init(void* workspace, size_t bytes, exl3_stream_t stream)
 {
     if (!workspace) return EXL3_E_NULL;
-    if (bytes < kWsPartials) return EXL3_E_WORKSPACE;
+    if (bytes < kWsScratch) return EXL3_E_WORKSPACE;
     if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
-    return note_cuda(cudaMemsetAsync(workspace, 0, kWsPartials, (cudaStream_t)stream));
+    return note_cuda(cudaMemsetAsync(workspace, 0, kWsScratch, (cudaStream_t)stream));
 }
 
 int exl3_workspace_status(const void* workspace, int* status_out, exl3_stream_t stream)
@@ -211,7 +210,7 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     if (k < 1 || k > 8) return EXL3_E_K;
     if (cb < 0 || cb > 2) return EXL3_E_CODEBOOK;
     if (t_in <= 0 || t_out <= 0 || t_in % 8 || t_out % 8) return EXL3_E_SHAPE;
-    if (t_out / 8 > kMaxCounters || t_in > (1 << 24) || t_out > (1 << 24)) return EXL3_E_SHAPE;
+    if (t_in > (1 << 24) || t_out > (1 << 24)) return EXL3_E_SHAPE;
     if (rows < 1 || rows > 16) return EXL3_E_ROWS;
     const int64_t in = 16 * t_in, out = 16 * t_out;
     if (x_row_stride < in || y_row_stride < out) return EXL3_E_SHAPE;
@@ -222,11 +221,11 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
         return EXL3_E_ALIGN;
     if (!workspace) return EXL3_E_WORKSPACE;
     if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
-    const size_t need = kWsPartials + ws_partial_bytes(rows) + (size_t)rows * in * 4;
+    const size_t need = kWsScratch + (size_t)rows * in * 4;
     if (workspace_bytes < need) return EXL3_E_WORKSPACE;
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    uint32_t* xh = reinterpret_cast<uint32_t*>(ws + kWsPartials + ws_partial_bytes(rows));
+    uint32_t* xh = reinterpret_cast<uint32_t*>(ws + kWsScratch);
     const bool pdl = (flags & EXL3_FLAG_PDL) != 0;
     const bool fast = (flags & EXL3_FLAG_FAST_ACCUM) != 0 && cb != CB_MUL1;
     cudaStream_t s = (cudaStream_t)stream;
@@ -246,8 +245,6 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     a.bias = reinterpret_cast<const __half*>(bias);
     a.y = reinterpret_cast<__half*>(y);
     a.blocks = nullptr;
-    a.partials = reinterpret_cast<float*>(ws + kWsPartials);
-    a.counters = reinterpret_cast<unsigned*>(ws + kWsCounters);
     a.status = reinterpret_cast<int*>(ws + kWsStatus);
     a.y_row_stride = y_row_stride;
     a.t_in = (int)t_in;
@@ -263,7 +260,7 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     a.x_dtype = x_dtype;
     a.x_fused = x_fused ? 1 : 0;
 #ifdef EXL3_PROFILE
-    a.prof = reinterpret_cast<long long*>(ws + kWsPartials);   // timing builds reuse the scratch area
+    a.prof = reinterpret_cast<long long*>(ws + kWsScratch);   // timing builds reuse the scratch area
 #endif
     return launch_gemv(a, k, cb, pdl, s);
 }
@@ -272,7 +269,7 @@ size_t exl3_gemm_workspace_bytes(int64_t rows, int64_t in)
 {
     if (rows < 1) rows = 1;
     if (in < 128) in = 128;
-    return ((size_t)kWsPartials + (size_t)rows * (size_t)in * 2 + 255) & ~(size_t)255;
+    return ((size_t)kWsScratch + (size_t)rows * (size_t)in * 2 + 255) & ~(size_t)255;
 }
 
 int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_stride, const uint16_t* trellis,
@@ -299,7 +296,7 @@ int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_stride, co
     if (workspace_bytes < exl3_gemm_workspace_bytes(rows, in)) return EXL3_E_WORKSPACE;
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    __half* xh = reinterpret_cast<__half*>(ws + kWsPartials);
+    __half* xh = reinterpret_cast<__half*>(ws + kWsScratch);
     cudaStream_t s = (cudaStream_t)stream;
     rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh), nullptr,
                          xh, nullptr, nullptr, nullptr, false, HAD_OUT_F16, s);

@@ -14,20 +14,11 @@ int note_cuda(cudaError_t e);       // records the error text; returns EXL3_OK o
 int check_launch();                 // note_cuda(cudaGetLastError())
 
 // ---- workspace layout ------------------------------------------------------------------------
-// [0, 256)                status word + padding
-// [256, 256 + 32 KiB)     per-column-block arrival counters (zero between launches)
-// [kWsPartials, ...)      split-K partial sums: kMaxCtas x 2 segments x rows x 128 floats
-// [...]                   rotated activations xh: rows x in fp16
+// [0, 256)      status word + padding (zero = no bounded wait ever gave up)
+// [256, ...)    scratch: the rotated activations xh of the current call — one 32-bit word per
+//               element for the GEMV when the rotation is not fused, fp16 for the GEMM
 constexpr size_t kWsStatus = 0;
-constexpr size_t kWsCounters = 256;
-constexpr int kMaxCounters = 8192;
-constexpr size_t kWsPartials = kWsCounters + (size_t)kMaxCounters * 4;
-constexpr int kMaxCtas = 1024;
-
-inline size_t ws_partial_bytes(int64_t rows_per_block)
-{
-    return (size_t)kMaxCtas * 2 * (size_t)rows_per_block * 128 * sizeof(float);
-}
+constexpr size_t kWsScratch = 256;
 
 // ---- launchers -------------------------------------------------------------------------------
 int launch_unpack(const uint32_t* trellis, int64_t n_tiles, int k, uint16_t* out, cudaStream_t s);
@@ -59,8 +50,6 @@ struct GemvArgs {
     const __half* bias;        // may be NULL
     __half* y;
     const ColBlock* blocks;    // may be NULL
-    float* partials;
-    unsigned* counters;
     int* status;
     int64_t y_row_stride;
     int t_in;                  // input tiles (multiple of 8)

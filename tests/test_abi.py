@@ -58,7 +58,7 @@ def test_host_side_validation_needs_no_gpu(lib):
     assert lib.exl3_decode(p, 1, 1, 4, 0, 1, 1, p, 16, None) == -10
     assert lib.exl3_hadamard128(p, 0, 1, 100, 100, None, None, p, None) == -4
     assert lib.exl3_hadamard128(p, 7, 1, 128, 128, None, None, p, None) == -8
-    assert lib.exl3_workspace_bytes(16, 17408) > lib.exl3_workspace_bytes(1, 4096) > 32768
+    assert lib.exl3_workspace_bytes(16, 17408) > lib.exl3_workspace_bytes(1, 4096) >= 256 + 4096 * 4
     gemv = lambda **kw: lib.exl3_gemv(
         kw.get("x", p), kw.get("dt", 0), kw.get("rows", 1), kw.get("xs", 128), kw.get("tr", p),
         kw.get("t_in", 8), kw.get("t_out", 8), kw.get("k", 4), kw.get("cb", 0), None, None, None,
