@@ -133,6 +133,29 @@ EXL3_API int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_s
               const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
               size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
 
+/* exl3_gemv without a caller-supplied workspace, for callers that cannot allocate device
+ * memory: operator slots of a serving framework or thin language bindings that are handed
+ * input and output buffers but own no allocator, and decode loops where cudaMalloc is
+ * forbidden or all free memory already belongs to someone else's pool.
+ * This entry point has no counterpart in the reference (unified memory there makes the
+ * question moot); it is an addition of this library.
+ *   - The scratch (status word + rotated activations) is a fixed device array inside the
+ *     library, 1 MiB + 256 B per GPU, held from library load until the process exits.
+ *   - Limit: rows * in_features <= 262,144 (e.g. 16 rows x 16,384 features); larger calls
+ *     return EXL3_E_RANGE and launch nothing.
+ *   - The first call on each device looks up the array's device address; make that first
+ *     call outside any stream capture.
+ *   - No cudaMalloc / cudaFree or allocating library routine is called.
+ *   - All calls on a device share the one array: calls that overlap on the GPU (different
+ *     streams) race on it; order them on one stream.  The array keeps the previous call's
+ *     contents; each call rewrites what it reads, and the status word stays sticky.
+ * Arguments and results are those of exl3_gemv. */
+EXL3_API int exl3_gemv_noalloc(const void* x, int x_dtype, int rows, int64_t x_row_stride,
+                               const uint16_t* trellis, int64_t t_in, int64_t t_out, int k, int cb,
+                               const uint16_t* suh, const uint16_t* svh, const uint16_t* bias,
+                               uint16_t* y, int64_t y_row_stride, unsigned flags,
+                               exl3_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
