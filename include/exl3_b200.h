@@ -121,6 +121,25 @@ EXL3_API int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_strid
               const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
               size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
 
+/* The streamed GEMV over a TABLE of 128-column blocks, for sibling groups and stacked MoE
+ * experts: block b multiplies `rows` rows of the rotated activations starting at row
+ * blocks[b].xrow with the trellis columns of physical block blocks[b].phys, scales with
+ * svh / adds bias at element offset blocks[b].sv_off (-1 = none) and stores its 128 outputs at
+ * element offset blocks[b].y_off of each y row.  `blocks` is a device array of n_blocks x
+ * {int32 phys, xrow, sv_off, y_off}.
+ * The rotated activations are xh_rows rows: row i = had(x[row_src[i]] * suh[suh_row[i]]),
+ * row_src / suh_row device int32 arrays or NULL (identity / row 0); suh is a (n, in) matrix.
+ * raw_out != 0 stores fp16(x @ W) without output rotation.
+ * Replaces the tile_map / tile_sub indirection of the reference's mapped GEMV:
+ * FusedEXL3Group.forward_all, ponyexl3/mlx/exl3_fused.py:136-202, and
+ * EXL3SwitchGLU._decode, ponyexl3/mlx/exl3_moe.py:634-683 (_mapped_gemv). */
+EXL3_API int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                     const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                     const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                     const int32_t* blocks, int64_t n_blocks, int rows, const uint16_t* svh,
+                     const uint16_t* bias, uint16_t* y, int64_t y_row_stride, int raw_out,
+                     void* workspace, size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
+
 /* Same contract for any number of rows (prefill): the packed tiles are decoded to fp16 in
  * shared memory and multiplied on the tensor cores (tcgen05.mma, fp32 accumulators in tensor
  * memory) against TMA-staged rotated activations; W is never materialised in global memory.

@@ -38,6 +38,10 @@ _PROTOTYPES = {
     "exl3_gemv": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_size_t,
                           c_uint, c_void_p]),
+    "exl3_gemv_blocks": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_size_t,
+                                 c_uint, c_void_p]),
     "exl3_gemm_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "exl3_gemm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_size_t,

@@ -265,6 +265,62 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     return launch_gemv(a, k, cb, pdl, s);
 }
 
+int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                     const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                     const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                     const int32_t* blocks, int64_t n_blocks, int rows, const uint16_t* svh,
+                     const uint16_t* bias, uint16_t* y, int64_t y_row_stride, int raw_out,
+                     void* workspace, size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+{
+    if (!x || !trellis || !y || !blocks) return EXL3_E_NULL;
+    if (k < 1 || k > 8) return EXL3_E_K;
+    if (cb < 0 || cb > 2) return EXL3_E_CODEBOOK;
+    if (t_in <= 0 || t_out_total <= 0 || t_in % 8 || t_out_total % 8) return EXL3_E_SHAPE;
+    if (t_in > (1 << 24) || t_out_total > (1 << 24)) return EXL3_E_SHAPE;
+    if (rows < 1 || rows > 16 || xh_rows < rows || xh_rows > (1 << 24)) return EXL3_E_ROWS;
+    if (n_blocks < 0 || n_blocks > (1 << 24)) return EXL3_E_SHAPE;
+    const int64_t in = 16 * t_in;
+    if (x_row_stride < in) return EXL3_E_SHAPE;
+    int rc = check_dtype_align(x, x_dtype, x_row_stride);
+    if (rc) return rc;
+    if (!aligned(trellis, 16) || !aligned(y, 8) || y_row_stride % 4 || !aligned(blocks, 16))
+        return EXL3_E_ALIGN;
+    if ((suh && !aligned(suh, 8)) || (svh && !aligned(svh, 8)) || (bias && !aligned(bias, 8)))
+        return EXL3_E_ALIGN;
+    if (!workspace) return EXL3_E_WORKSPACE;
+    if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
+    if (workspace_bytes < kWsScratch + (size_t)xh_rows * in * 4) return EXL3_E_WORKSPACE;
+    if (n_blocks == 0) return EXL3_OK;
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    uint32_t* xh = reinterpret_cast<uint32_t*>(ws + kWsScratch);
+    const bool pdl = (flags & EXL3_FLAG_PDL) != 0;
+    const bool fast = (flags & EXL3_FLAG_FAST_ACCUM) != 0 && cb != CB_MUL1;
+    cudaStream_t s = (cudaStream_t)stream;
+    rc = launch_hadamard(x, x_dtype, xh_rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
+                         nullptr, reinterpret_cast<__half*>(xh), row_src, suh_row, nullptr, pdl,
+                         fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s);
+    if (rc) return rc;
+    GemvArgs a = {};
+    a.trellis = reinterpret_cast<const uint32_t*>(trellis);
+    a.xh = xh;
+    a.svh = reinterpret_cast<const __half*>(svh);
+    a.bias = reinterpret_cast<const __half*>(bias);
+    a.y = reinterpret_cast<__half*>(y);
+    a.blocks = reinterpret_cast<const ColBlock*>(blocks);
+    a.status = reinterpret_cast<int*>(ws + kWsStatus);
+    a.y_row_stride = y_row_stride;
+    a.t_in = (int)t_in;
+    a.t_out_total = (int)t_out_total;
+    a.ncb = (int)n_blocks;
+    a.rows = rows;
+    a.x_rows_total = (int)xh_rows;
+    a.raw_out = raw_out ? 1 : 0;
+    a.fast_accum = fast ? 1 : 0;
+    a.x_fused = 0;
+    return launch_gemv(a, k, cb, pdl, s);
+}
+
 size_t exl3_gemm_workspace_bytes(int64_t rows, int64_t in)
 {
     if (rows < 1) rows = 1;

@@ -1,0 +1,183 @@
+"""EXL3 MoE experts — stacked-expert SwitchGLU and the routed block around it.
+
+Mirrors ``EXL3SwitchGLU`` / ``EXL3MoEBlock`` of the reference
+(ponyexl3/mlx/exl3_moe.py:425-839).  Per layer the expert trellises are stacked along the
+out-tile axis into ONE device buffer — ``gu_trellis (D/16, E*2*H/16, 16K)`` holds all gates,
+then all ups; ``dn_trellis (H/16, E*D/16, 16K)`` — with per-expert sign vectors
+``gu_suh (E, 2, D)``, ``gu_svh (E, 2H)``, ``dn_suh (E, H)``, ``dn_svh (E, D)``.
+
+``__call__(x (B, S, D), indices (B, S, k)) -> (B, S, k, D)``: un-weighted expert outputs, as
+mlx_lm's SwitchGLU; routing and the weighted sum stay in the block.
+
+Decode-class calls (few tokens) run two streamed GEMVs over block tables built on the device
+from the routing indices — every (token, slot) pair is its own one-row problem against its
+expert's column range (the reference's mapped GEMV, exl3_moe.py:634-683).  Prefill-class
+calls sort the pairs by expert and run the tensor-core GEMM per expert segment.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+_ACTIVATIONS = ("silu", "gelu")
+DECODE_MAX_TOKENS = 16
+
+
+def glu(g: torch.Tensor, u: torch.Tensor, activation: str) -> torch.Tensor:
+    """fp16( act(g) * u ), float32 math (ponyexl3/mlx/exl3_moe.py:62-75)."""
+    g32, u32 = g.float(), u.float()
+    if activation == "gelu":
+        h = 0.5 * g32 * (1.0 + torch.tanh(0.797884560803 * (g32 + 0.044715 * g32 * g32 * g32))) * u32
+    else:
+        h = (g32 / (1.0 + torch.exp(-g32))) * u32
+    return h.to(torch.float16)
+
+
+class EXL3SwitchGLU(torch.nn.Module):
+    """Stacked-expert EXL3 SwitchGLU (gate+up per expert, then down)."""
+
+    def __init__(self, *, gu_trellis: torch.Tensor, gu_suh: torch.Tensor, gu_svh: torch.Tensor,
+                 dn_trellis: torch.Tensor, dn_suh: torch.Tensor, dn_svh: torch.Tensor, k: int, cb: int,
+                 activation: str = "silu"):
+        super().__init__()
+        if activation not in _ACTIVATIONS:
+            raise ValueError(f"unsupported MoE activation {activation!r}")
+        if not gu_trellis.is_cuda:
+            raise RuntimeError("EXL3SwitchGLU needs CUDA tensors: there is no CPU path")
+        self.num_experts = int(gu_suh.shape[0])
+        self.input_dims = int(gu_suh.shape[2])
+        self.hidden_dims = int(dn_suh.shape[1])
+        E, D, H = self.num_experts, self.input_dims, self.hidden_dims
+        if D % 128 or H % 128:
+            raise ValueError("expert dims must be multiples of 128")
+        if tuple(gu_trellis.shape) != (D // 16, E * 2 * H // 16, 16 * k):
+            raise ValueError(f"gu_trellis shape {tuple(gu_trellis.shape)} does not fit E={E} D={D} H={H} K={k}")
+        if tuple(dn_trellis.shape) != (H // 16, E * D // 16, 16 * k):
+            raise ValueError(f"dn_trellis shape {tuple(dn_trellis.shape)} does not fit E={E} D={D} H={H} K={k}")
+        if tuple(gu_svh.shape) != (E, 2 * H) or tuple(dn_svh.shape) != (E, D) or tuple(dn_suh.shape) != (E, H):
+            raise ValueError("sign vector shapes do not fit the expert dims")
+        self.k, self.cb, self.activation = int(k), int(cb), activation
+        self._gu_trellis = gu_trellis.contiguous()
+        self._dn_trellis = dn_trellis.contiguous()
+        self._gu_suh = gu_suh.to(torch.float16).reshape(E * 2, D).contiguous()
+        self._gu_svh = gu_svh.to(torch.float16).reshape(-1).contiguous()
+        self._dn_suh = dn_suh.to(torch.float16).contiguous()
+        self._dn_svh = dn_svh.to(torch.float16).reshape(-1).contiguous()
+        self.pdl = False
+
+    # ---- decode: every (token, slot) pair is a one-row problem -------------------------------
+    def _decode(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        E, D, H = self.num_experts, self.input_dims, self.hidden_dims
+        R, kk = indices.shape
+        n = R * kk
+        dev = x2d.device
+        sel = indices.reshape(-1).to(torch.int32)                    # expert of slot s
+        slot = torch.arange(n, device=dev, dtype=torch.int32)
+        tok = slot // kk
+
+        # gate + up: rotated row 2s+p = had(x[tok(s)] * gu_suh[e_s, p]); block (s, p, j)
+        gb, db = H // 128, D // 128
+        p = torch.arange(2, device=dev, dtype=torch.int32).view(1, 2, 1)
+        j = torch.arange(gb, device=dev, dtype=torch.int32).view(1, 1, gb)
+        s3, e3 = slot.view(n, 1, 1), sel.view(n, 1, 1)
+        phys = (p * E + e3) * gb + j
+        xrow = (2 * s3 + p).expand(n, 2, gb)
+        sv = e3 * (2 * H) + p * H + 128 * j
+        yo = s3 * (2 * H) + p * H + 128 * j
+        blocks = torch.stack([phys, xrow, sv, yo], dim=-1).reshape(-1, 4).contiguous()
+        row_src = tok.repeat_interleave(2)
+        suh_row = (sel.view(n, 1) * 2 + torch.arange(2, device=dev, dtype=torch.int32)).reshape(-1)
+        ygu = torch.empty(n * 2 * H, dtype=torch.float16, device=dev)
+        ops.gemv_blocks(x2d, xh_rows=2 * n, row_src=row_src.contiguous(), suh=self._gu_suh,
+                        suh_row=suh_row.contiguous(), trellis=self._gu_trellis, k=self.k, cb=self.cb,
+                        blocks=blocks, rows=1, svh=self._gu_svh, bias=None, y=ygu, pdl=self.pdl)
+        ygu = ygu.view(n, 2 * H)
+        h = glu(ygu[:, :H], ygu[:, H:], self.activation)
+
+        # down: rotated row s = had(h[s] * dn_suh[e_s]); block (s, j)
+        jd = torch.arange(db, device=dev, dtype=torch.int32).view(1, db)
+        s2, e2 = slot.view(n, 1), sel.view(n, 1)
+        blocks = torch.stack([e2 * db + jd, s2.expand(n, db), e2 * D + 128 * jd, s2 * D + 128 * jd],
+                             dim=-1).reshape(-1, 4).contiguous()
+        y = torch.empty(n * D, dtype=torch.float16, device=dev)
+        ops.gemv_blocks(h, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=sel.contiguous(),
+                        trellis=self._dn_trellis, k=self.k, cb=self.cb, blocks=blocks, rows=1,
+                        svh=self._dn_svh, bias=None, y=y, pdl=self.pdl)
+        return y.view(R, kk, D)
+
+    # ---- prefill: pairs sorted by expert, one GEMM per expert segment ----------------------------
+    def _prefill(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        E, D, H = self.num_experts, self.input_dims, self.hidden_dims
+        R, kk = indices.shape
+        flat = indices.reshape(-1).to(torch.int64)
+        order = torch.argsort(flat, stable=True)
+        sidx = flat[order]
+        tok = torch.div(order, kk, rounding_mode="floor")
+        counts = torch.bincount(sidx, minlength=E).cpu().tolist()       # segment sizes (host)
+        xs = x2d[tok]
+        out = torch.empty((R * kk, D), dtype=torch.float16, device=x2d.device)
+        gu_suh = self._gu_suh.view(E, 2, D)
+        gu_svh = self._gu_svh.view(E, 2 * H)
+        dn_svh = self._dn_svh.view(E, D)
+        gt, dt = H // 16, D // 16
+        r0 = 0
+        for e, c in enumerate(counts):
+            if c == 0:
+                continue
+            xe = xs[r0:r0 + c]
+            fwd = ops.gemm if c > 16 else ops.gemv
+            g = fwd(xe, self._gu_trellis[:, e * gt:(e + 1) * gt].contiguous(), self.k, self.cb,
+                    gu_suh[e, 0], gu_svh[e, :H], None)
+            u = fwd(xe, self._gu_trellis[:, (E + e) * gt:(E + e + 1) * gt].contiguous(), self.k, self.cb,
+                    gu_suh[e, 1], gu_svh[e, H:], None)
+            h = glu(g, u, self.activation)
+            fwd(h, self._dn_trellis[:, e * dt:(e + 1) * dt].contiguous(), self.k, self.cb,
+                self._dn_suh[e], dn_svh[e], None, out=out[r0:r0 + c])
+            r0 += c
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=order.device)
+        return out[inv].view(R, kk, D)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        if indices.ndim != 3:
+            raise ValueError("indices must be (B, S, k)")
+        B, S, kk = indices.shape
+        R = B * S
+        x2d = x.reshape(R, self.input_dims)
+        idx = indices.reshape(R, kk)
+        y = self._decode(x2d, idx) if R <= DECODE_MAX_TOKENS else self._prefill(x2d, idx)
+        return y.reshape(B, S, kk, self.input_dims)
+
+
+def route_topk(logits: torch.Tensor, top_k: int, norm_topk_prob: bool = True):
+    """softmax -> top-k -> renormalise (ponyexl3/mlx/exl3_moe.py:807-831): indices, scores."""
+    gates = torch.softmax(logits.float(), dim=-1)
+    scores, inds = torch.topk(gates, top_k, dim=-1)
+    if norm_topk_prob:
+        scores = scores / scores.sum(dim=-1, keepdim=True)
+    return inds, scores
+
+
+class EXL3MoEBlock(torch.nn.Module):
+    """Router + stacked experts + weighted sum (ponyexl3/mlx/exl3_moe.py:790-839, without the
+    shared-expert slot, which is one more expert index for the switch)."""
+
+    def __init__(self, gate_weight: torch.Tensor, switch: EXL3SwitchGLU, top_k: int,
+                 norm_topk_prob: bool = True):
+        super().__init__()
+        self.gate_weight = gate_weight          # (E, D) router, unquantised
+        self.switch_mlp = switch
+        self.top_k = top_k
+        self.norm_topk_prob = norm_topk_prob
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x3 = x.reshape(1, -1, x.shape[-1])
+        inds, scores = route_topk(x3.float() @ self.gate_weight.float().t(), self.top_k,
+                                  self.norm_topk_prob)
+        y = self.switch_mlp(x3, inds)
+        return (y.float() * scores[..., None]).sum(dim=-2).to(torch.float16).reshape(lead + (x.shape[-1],))

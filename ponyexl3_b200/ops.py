@@ -201,3 +201,32 @@ def gemm(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh: torch.T
         None if svh is None else svh.data_ptr(), None if bias is None else bias.data_ptr(),
         y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes, 0, _stream(x2d.device)), "exl3_gemm")
     return y
+
+
+def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None,
+                suh: torch.Tensor | None, suh_row: torch.Tensor | None, trellis: torch.Tensor, k: int,
+                cb: int, blocks: torch.Tensor, rows: int, svh: torch.Tensor | None,
+                bias: torch.Tensor | None, y: torch.Tensor, raw_out: bool = False, pdl: bool = False,
+                fast_accum: bool = False) -> torch.Tensor:
+    """Streamed GEMV over a block table (see exl3_gemv_blocks in the header).  `blocks` is an
+    int32 CUDA tensor (n_blocks, 4) = phys, xrow, sv_off, y_off; `y` is written in place."""
+    _need_cuda(x2d, "x")
+    t_in, t_out_total, _ = trellis.shape
+    if x2d.shape[1] != t_in * 16:
+        raise ValueError(f"x has {x2d.shape[1]} features, layer expects {t_in * 16}")
+    if blocks.dtype != torch.int32 or blocks.ndim != 2 or blocks.shape[1] != 4:
+        raise ValueError("blocks must be an int32 tensor of shape (n_blocks, 4)")
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    blocks = blocks.contiguous()
+    lib = _lib.load()
+    ws = Workspace.get_bytes(x2d.device, 256 + xh_rows * t_in * 16 * 4)
+    ptr = lambda t: None if t is None else t.data_ptr()
+    _lib.check(lib.exl3_gemv_blocks(
+        x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),
+        ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), blocks.data_ptr(),
+        blocks.shape[0], rows, ptr(svh), ptr(bias), y.data_ptr(), y.stride(0) if y.ndim == 2 else 0,
+        1 if raw_out else 0, ws.buf.data_ptr(), ws.nbytes,
+        (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0),
+        _stream(x2d.device)), "exl3_gemv_blocks")
+    return y

@@ -1,0 +1,183 @@
+"""Sharding of the EXL3 path over the GPUs of one box (one process per GPU, torch.distributed).
+
+The reference is single-device; what has to hold here is only that the sharded result
+equals the unsharded one.
+
+* Dense linear — tensor parallel by OUTPUT TILE.  Tiles are independent and stored
+  ``[in_tile][out_tile]``, so a rank's shard is a column slice of the packed trellis with no
+  re-encoding.  Shards are whole 128-column blocks, which keeps the output Hadamard rotation,
+  ``svh`` and ``bias`` local; every rank needs the whole input row and the whole ``suh``.  The
+  per-rank outputs are all-gathered (NCCL on GPUs, gloo in the CPU tests).
+* Stacked MoE experts — expert parallel: rank g owns a contiguous range of experts (a
+  contiguous out-tile range of the stacked trellises).  Decode-class calls replicate the few
+  tokens, every rank computes the (token, slot) pairs whose expert it owns and the partial
+  outputs are summed (all-reduce); prefill-class calls with tokens partitioned over the ranks
+  exchange rows with two all-to-alls.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .layer import EXL3Layer, unpack_signs_or_pass
+
+
+def shard_blocks(n_blocks: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous block range [b0, b1) of `rank`; the first n_blocks % world ranks get one more."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    base, extra = divmod(n_blocks, world)
+    b0 = rank * base + min(rank, extra)
+    return b0, b0 + base + (1 if rank < extra else 0)
+
+
+def shard_columns(out_features: int, world: int, rank: int) -> tuple[int, int]:
+    """Column range of `rank` under tensor parallelism by output tile (multiples of 128)."""
+    if out_features % 128:
+        raise ValueError("out_features must be a multiple of 128")
+    b0, b1 = shard_blocks(out_features // 128, world, rank)
+    return b0 * 128, b1 * 128
+
+
+def shard_layer(layer: EXL3Layer, world: int, rank: int) -> EXL3Layer:
+    """The column shard of `layer` owned by `rank` (may be empty when world > blocks)."""
+    c0, c1 = shard_columns(layer.out_features, world, rank)
+    svh = unpack_signs_or_pass(layer.svh)
+    return EXL3Layer(
+        key=f"{layer.key}[tp{rank}/{world}]", in_features=layer.in_features, out_features=c1 - c0,
+        k=layer.k, trellis=np.ascontiguousarray(layer.trellis[:, c0 // 16:c1 // 16]), suh=layer.suh,
+        svh=None if svh is None else svh[c0:c1],
+        bias=None if layer.bias is None else layer.bias[c0:c1], mcg=layer.mcg, mul1=layer.mul1)
+
+
+def all_gather_columns(y_local: torch.Tensor, out_features: int, group=None) -> torch.Tensor:
+    """(rows, local_cols) on every rank -> (rows, out_features) on every rank, for the uneven
+    128-block split of shard_columns."""
+    world = dist.get_world_size(group)
+    rows = y_local.shape[0]
+    if (out_features // 128) % world == 0:
+        full = torch.empty((world, rows, out_features // world), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(full.view(-1), y_local.contiguous().view(-1), group=group)
+        return full.permute(1, 0, 2).reshape(rows, out_features)
+    # uneven split (e.g. 1187 blocks over 8 ranks): pad every shard to the widest, gather, cut
+    spans = [shard_columns(out_features, world, r) for r in range(world)]
+    wmax = max(c1 - c0 for c0, c1 in spans)
+    padded = torch.zeros((rows, wmax), dtype=y_local.dtype, device=y_local.device)
+    padded[:, :y_local.shape[1]] = y_local
+    full = torch.empty((world, rows, wmax), dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(full.view(-1), padded.view(-1), group=group)
+    return torch.cat([full[r, :, :c1 - c0] for r, (c0, c1) in enumerate(spans)], dim=1)
+
+
+class TPLinear(torch.nn.Module):
+    """A linear layer sharded by output tile: local forward on this rank's columns, then an
+    all-gather.  `local` is this rank's module (an EXL3Linear built from shard_layer)."""
+
+    def __init__(self, local: Callable[[torch.Tensor], torch.Tensor], out_features: int, group=None):
+        super().__init__()
+        self.__dict__["local"] = local
+        self.out_features = out_features
+        self.group = group
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        y = self.local(x.reshape(-1, x.shape[-1]))
+        return all_gather_columns(y, self.out_features, self.group).reshape(lead + (self.out_features,))
+
+
+# ---- expert parallel ---------------------------------------------------------------------------
+
+def shard_experts(num_experts: int, world: int, rank: int) -> tuple[int, int]:
+    """Expert range [e0, e1) of `rank`."""
+    return shard_blocks(num_experts, world, rank)
+
+
+def shard_expert_weights(w: dict, num_experts: int, world: int, rank: int) -> dict:
+    """Slice stacked expert tensors (numpy or torch) to this rank's experts.  The stacked
+    gate/up trellis holds all gates, then all ups, so the shard is two column ranges."""
+    e0, e1 = shard_experts(num_experts, world, rank)
+    gu = w["gu_trellis"]
+    gt = gu.shape[1] // (2 * num_experts)
+    dt = w["dn_trellis"].shape[1] // num_experts
+    cat = np.concatenate if isinstance(gu, np.ndarray) else (lambda xs, axis: torch.cat(xs, dim=axis))
+    return dict(
+        gu_trellis=cat([gu[:, e0 * gt:e1 * gt], gu[:, (num_experts + e0) * gt:(num_experts + e1) * gt]], 1),
+        gu_suh=w["gu_suh"][e0:e1], gu_svh=w["gu_svh"][e0:e1],
+        dn_trellis=w["dn_trellis"][:, e0 * dt:e1 * dt], dn_suh=w["dn_suh"][e0:e1], dn_svh=w["dn_svh"][e0:e1])
+
+
+class EPSwitchGLU(torch.nn.Module):
+    """Stacked experts sharded by expert.  `local(x (1,T,D), idx (1,T,k)) -> (1,T,k,D)` is this
+    rank's switch over its own experts (local indices); tokens are replicated on every rank.
+    Pairs routed to another rank's expert are computed there; the partial outputs are summed."""
+
+    def __init__(self, local: Callable, num_experts: int, group=None):
+        super().__init__()
+        self.__dict__["local"] = local
+        self.num_experts = num_experts
+        self.group = group
+
+    def forward(self, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        e0, e1 = shard_experts(self.num_experts, world, rank)
+        B, S, kk = indices.shape
+        D = x.shape[-1]
+        flat = indices.reshape(-1)
+        mine = (flat >= e0) & (flat < e1)
+        out = torch.zeros((B * S * kk, D), dtype=torch.float16, device=x.device)
+        sel = torch.nonzero(mine).reshape(-1)                 # pairs this rank computes
+        if sel.numel() > 0:
+            tok = torch.div(sel, kk, rounding_mode="floor")
+            xs = x.reshape(B * S, D)[tok]
+            # every selected pair becomes a one-slot token for the local switch
+            y = self.local(xs.reshape(1, -1, D), (flat[sel] - e0).reshape(1, -1, 1))
+            out[sel] = y.reshape(-1, D).to(torch.float16)
+        # each pair is written by exactly one rank and is zero elsewhere, so the fp16 sum is exact
+        if out.device.type == "cpu":      # gloo has no fp16 reduction
+            out32 = out.float()
+            dist.all_reduce(out32, group=self.group)
+            out = out32.to(torch.float16)
+        else:
+            dist.all_reduce(out, group=self.group)
+        return out.reshape(B, S, kk, D)
+
+
+def dispatch_rows_to_experts(x_local: torch.Tensor, idx_local: torch.Tensor, num_experts: int, group=None):
+    """Prefill exchange, step 1: tokens are partitioned over the ranks; every (token, slot) row
+    goes to the rank that owns its expert.  Returns (rows received, their local expert index,
+    the bookkeeping needed by return_rows_to_tokens)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    T, kk = idx_local.shape
+    flat = idx_local.reshape(-1)
+    bounds = torch.tensor([shard_experts(num_experts, world, r)[1] for r in range(world)],
+                          device=flat.device)
+    owner = torch.searchsorted(bounds, flat, right=True)
+    order = torch.argsort(owner, stable=True)
+    send_counts = torch.bincount(owner, minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    sc, rc = send_counts.cpu().tolist(), recv_counts.cpu().tolist()
+    rows = x_local[torch.div(order, kk, rounding_mode="floor")].contiguous()
+    recv = torch.empty((sum(rc), x_local.shape[1]), dtype=x_local.dtype, device=x_local.device)
+    dist.all_to_all_single(recv, rows, output_split_sizes=rc, input_split_sizes=sc, group=group)
+    e_send = flat[order].contiguous()
+    e_recv = torch.empty((sum(rc),), dtype=e_send.dtype, device=e_send.device)
+    dist.all_to_all_single(e_recv, e_send, output_split_sizes=rc, input_split_sizes=sc, group=group)
+    e0 = shard_experts(num_experts, world, rank)[0]
+    return recv, e_recv - e0, (order, sc, rc, T, kk)
+
+
+def return_rows_to_tokens(y_rows: torch.Tensor, book, group=None) -> torch.Tensor:
+    """Prefill exchange, step 2: expert outputs travel back to the rank that owns the token;
+    returns (T_local, k, D) in the original (token, slot) order."""
+    order, sc, rc, T, kk = book
+    back = torch.empty((sum(sc), y_rows.shape[1]), dtype=y_rows.dtype, device=y_rows.device)
+    dist.all_to_all_single(back, y_rows.contiguous(), output_split_sizes=sc, input_split_sizes=rc,
+                           group=group)
+    out = torch.empty_like(back)
+    out[order] = back
+    return out.reshape(T, kk, -1)

@@ -1,0 +1,135 @@
+"""GPU parity of the block-table GEMV users: fused sibling groups and the stacked-expert
+SwitchGLU (decode and prefill paths), against the CPU oracle.  Tolerance 1e-3 relative L2 per
+linear; the MoE chain (gate/up -> GLU -> down) is checked at 2e-3, as two roundings chain."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from conftest import rel_err, synthetic_layer
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda")
+
+
+def _members(k, inf, outs, seed, cb=0):
+    import ponyexl3_b200
+    layers = []
+    for i, o in enumerate(outs):
+        tr, suh, svh, _ = synthetic_layer(k, inf, o, seed + i)
+        layers.append(ponyexl3_b200.EXL3Layer(f"m{i}", inf, o, k, tr, suh, svh, None,
+                                              mcg=(cb == 1), mul1=(cb == 2)))
+    return layers
+
+
+@pytest.mark.parametrize("rows", [1, 8, 16, 19])
+@pytest.mark.parametrize("k,cb", [(4, 0), (3, 1), (6, 2)])
+def test_fused_group_matches_members(cuda, oracle, rows, k, cb):
+    """Rows {1, 8, 19} as the reference's group test (tests/test_exl3_fused.py:31-45)."""
+    from ponyexl3_b200.fused import FusedEXL3Group
+
+    layers = _members(k, 512, [512, 128, 256], seed=900 + k, cb=cb)
+    grp = FusedEXL3Group(layers)
+    x = np.random.default_rng(rows).standard_normal((rows, 512)).astype(np.float16)
+    outs = grp.forward_all(torch.from_numpy(x).cuda())
+    assert len(outs) == 3
+    for o, l in zip(outs, layers):
+        want = oracle.linear_forward(x, l.trellis, l.k, l.codebook_mode, l.suh, l.svh, None)
+        assert o.shape == want.shape
+        assert rel_err(o.cpu().numpy(), want) <= 1e-3
+
+
+def test_fused_siblings_share_one_launch_and_refuse_bad_groups(cuda):
+    from ponyexl3_b200.fused import FusedEXL3Group, fusable
+
+    layers = _members(4, 256, [256, 128], seed=950)
+    grp = FusedEXL3Group(layers)
+    q, kproj = grp.sibling(0), grp.sibling(1)
+    x = torch.randn((1, 256), device="cuda").half()
+    a = q(x)
+    assert grp._cache_x is x
+    b = kproj(x)
+    assert a.shape == (1, 256) and b.shape == (1, 128)
+    assert list(grp.parameters()) == []
+    bad = _members(4, 256, [256, 128], seed=951)
+    bad[1].k = 5
+    assert not fusable(bad)
+    with pytest.raises(ValueError):
+        FusedEXL3Group(bad)
+
+
+def _experts(E, D, H, k, seed):
+    rng = np.random.default_rng(seed)
+    gu = rng.integers(0, 65536, size=(D // 16, E * 2 * H // 16, 16 * k), dtype=np.uint16)
+    dn = rng.integers(0, 65536, size=(H // 16, E * D // 16, 16 * k), dtype=np.uint16)
+    sg = lambda *s: np.where(rng.random(s) > 0.5, -1.0, 1.0).astype(np.float16)
+    return dict(gu_trellis=gu, gu_suh=sg(E, 2, D), gu_svh=sg(E, 2 * H), dn_trellis=dn,
+                dn_suh=sg(E, H), dn_svh=sg(E, D))
+
+
+def _switch(w, k, cb, act="silu"):
+    from ponyexl3_b200.moe import EXL3SwitchGLU
+
+    t = {n: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda() for n, a in w.items()}
+    for n in ("gu_suh", "gu_svh", "dn_suh", "dn_svh"):
+        t[n] = t[n].view(torch.float16)
+    return EXL3SwitchGLU(**t, k=k, cb=cb, activation=act)
+
+
+@pytest.mark.parametrize("tokens", [1, 3, 16])
+@pytest.mark.parametrize("k,cb,act", [(4, 0, "silu"), (3, 1, "gelu")])
+def test_switch_glu_decode_matches_oracle(cuda, oracle, tokens, k, cb, act):
+    E, D, H, kk = 8, 256, 128, 2
+    w = _experts(E, D, H, k, seed=40 + k)
+    sw = _switch(w, k, cb, act)
+    rng = np.random.default_rng(tokens)
+    x = (rng.standard_normal((tokens, D)) * 0.5).astype(np.float16)
+    idx = np.stack([rng.choice(E, size=kk, replace=False) for _ in range(tokens)]).astype(np.int64)
+    y = sw(torch.from_numpy(x).cuda().view(1, tokens, D), torch.from_numpy(idx).cuda().view(1, tokens, kk))
+    assert y.shape == (1, tokens, kk, D)
+    want = oracle.switch_glu(x, idx, **w, k=k, cb=cb, activation=act)
+    assert rel_err(y.cpu().numpy().reshape(tokens, kk, D), want) <= 2e-3
+
+
+def test_switch_glu_prefill_matches_oracle_and_decode(cuda, oracle):
+    E, D, H, kk, k = 8, 256, 128, 2, 4
+    w = _experts(E, D, H, k, seed=77)
+    sw = _switch(w, k, 0)
+    rng = np.random.default_rng(5)
+    T = 150
+    x = (rng.standard_normal((T, D)) * 0.5).astype(np.float16)
+    idx = np.stack([rng.choice(E, size=kk, replace=False) for _ in range(T)]).astype(np.int64)
+    y = sw(torch.from_numpy(x).cuda().view(1, T, D), torch.from_numpy(idx).cuda().view(1, T, kk))
+    want = oracle.switch_glu(x, idx, **w, k=k, cb=0)
+    assert rel_err(y.cpu().numpy().reshape(T, kk, D), want) <= 2e-3
+
+
+def test_config4_moe_block_one_token(cuda, oracle):
+    """256 experts, top-8, hidden 2048, expert intermediate 512, K = 4: one token through router,
+    stacked experts and weighted sum; expert outputs checked against the oracle."""
+    from ponyexl3_b200.moe import EXL3MoEBlock, route_topk
+
+    E, D, H, kk, k = 256, 2048, 512, 8, 4
+    w = _experts(E, D, H, k, seed=4000)
+    sw = _switch(w, k, 0)
+    rng = np.random.default_rng(4001)
+    x = (rng.standard_normal((1, D)) * 0.5).astype(np.float16)
+    logits = rng.standard_normal((1, E)).astype(np.float32)
+    inds, scores = route_topk(torch.from_numpy(logits).cuda(), kk)
+    assert abs(float(scores.sum()) - 1.0) < 1e-5
+    y = sw(torch.from_numpy(x).cuda().view(1, 1, D), inds.view(1, 1, kk))
+    want = oracle.switch_glu(x, inds.cpu().numpy(), **w, k=k, cb=0)
+    assert rel_err(y.cpu().numpy().reshape(1, kk, D), want) <= 2e-3
+    gate_w = torch.from_numpy(rng.standard_normal((E, D)).astype(np.float32) * 0.05).cuda()
+    blk = EXL3MoEBlock(gate_w, sw, kk)
+    out = blk(torch.from_numpy(x).cuda())
+    assert out.shape == (1, D) and torch.isfinite(out.float()).all()
