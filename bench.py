@@ -176,12 +176,9 @@ def run_reference(args):
 # ------------------------------------------------------------------------ GPU arm -----
 
 def shard_cols(outf: int, world: int, rank: int):
-    """Contiguous range of 128-column blocks owned by `rank` (tensor parallel by output tile)."""
-    nblk = outf // 128
-    base, extra = divmod(nblk, world)
-    b0 = rank * base + min(rank, extra)
-    b1 = b0 + base + (1 if rank < extra else 0)
-    return b0 * 128, b1 * 128
+    """Column range owned by `rank` (tensor parallel by output tile, whole 128-column blocks)."""
+    from ponyexl3_b200.parallel import shard_columns
+    return shard_columns(outf, world, rank)
 
 
 def run_gpu(args):
@@ -199,7 +196,8 @@ def run_gpu(args):
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
 
     from ponyexl3_b200 import EXL3Layer, _lib, ops
     from ponyexl3_b200.linear import EXL3Linear
@@ -229,22 +227,24 @@ def run_gpu(args):
             step_bytes_global += packed_bytes((inf, outf))
     xs = {inf: torch.randn((ROWS, inf), device=dev, generator=gen).to(torch.float16)
           for inf in {s[0] for s in SHAPES}}
-    uneven = any((L.outf // 128) % world for L in layers)
+    from ponyexl3_b200.parallel import all_gather_columns
 
-    def one_layer(L, x, pdl=True):
-        ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=pdl, out=L.y)
+    def one_layer(L, x):
+        # programmatic launch only on one GPU: between NCCL kernels plain stream order is kept
+        ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=(dist is None), out=L.y)
         if dist is not None:
-            if uneven:
-                parts = [L.y_full[:, slice(*shard_cols(L.outf, world, r))] for r in range(world)]
-                dist.all_gather([p.contiguous() for p in parts], L.y)
-            else:
+            if ROWS == 1 and (L.outf // 128) % world == 0:
+                # one row, even split: the gathered chunks ARE the full row, no reshuffle
                 dist.all_gather_into_tensor(L.y_full.view(-1), L.y.view(-1))
+            else:
+                L.y_full = all_gather_columns(L.y, L.outf)
 
     def step_body():
         for L in layers:
             one_layer(L, xs[L.inf])
 
     stream = torch.cuda.Stream(device=dev)
+    # NCCL all-gathers are captured with the kernels; every rank captures the same sequence
     use_graph = not args.no_graph
     graph = None
     with torch.cuda.stream(stream):
@@ -256,6 +256,8 @@ def run_gpu(args):
                 with torch.cuda.graph(graph, stream=stream):
                     step_body()
             except Exception as e:  # capture not possible: run the launches eagerly
+                if dist is not None:
+                    raise       # ranks must not diverge (graph on one, eager on another)
                 graph = None
                 torch.cuda.synchronize()
                 if rank == 0:
@@ -287,9 +289,10 @@ def run_gpu(args):
         e1.record(stream)
         barrier()
         ms = e0.elapsed_time(e1)
-        # keep the GPU under the same load a little longer so the clock sampler sees it
-        t_end = time.perf_counter() + 0.25
-        while time.perf_counter() < t_end:
+        # keep the GPU under the same load a little longer so the clock sampler sees it; a
+        # fixed step count, because every rank must issue the same number of collectives
+        extra = max(args.steps, int(250.0 / max(ms / args.steps, 1e-3))) if dist is None else args.steps
+        for _ in range(min(extra, 2000)):
             run_step()
         torch.cuda.synchronize()
         clocks = sampler.stop()
@@ -304,7 +307,8 @@ def run_gpu(args):
     for L in layers:
         m = EXL3Linear.from_device_tensors(trellis=L.trellis, k=K_BITS, cb=CB, suh=L.suh, svh=L.svh,
                                            key="bench")
-        m.pdl = True
+        m.pdl = dist is None
+        m.full_out = L.outf
         mods.append(m)
     h_in = {inf: torch.randn((ROWS, inf)).to(torch.float16).pin_memory() for inf in xs}
     d_in = {inf: torch.empty_like(xs[inf]) for inf in xs}
@@ -316,7 +320,10 @@ def run_gpu(args):
         for inf in h_in:
             d_in[inf].copy_(h_in[inf], non_blocking=True)
         for m, ho in zip(mods, h_out):
-            ho.copy_(m(d_in[m.in_features]), non_blocking=True)
+            y_loc = m(d_in[m.in_features])
+            if dist is not None:
+                all_gather_columns(y_loc, m.full_out)
+            ho.copy_(y_loc, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = max(3, min(args.steps, 20))
@@ -373,15 +380,15 @@ def run_gpu(args):
                 "bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                 "frac": per_gpu / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
                 "kernel": "exl3::gemv_kernel<4,0,1>",
-                "note": "achieved = packed bytes per launch / (step time / GEMV launches); the step "
-                        "time also holds the small rotation kernels",
+                "note": "achieved = packed bytes per launch / (step time / GEMV launches); both "
+                        "rotations run inside the GEMV kernel",
                 "avg_launch_us": 1e3 * ms / args.steps / n_gemv,
             },
             "cpu_baseline": cpu,
             "e2e": {"value": step_bytes_global / e2e_s / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": 1e3 * e2e_s, "api": "EXL3Linear.forward per layer, pinned host x and y"},
-            "gpu_launches": 2 * n_gemv * args.steps,
+            "gpu_launches": n_gemv * args.steps,  # one fused kernel per layer (rotation inside)
             "clocks": clocks,
             "kernel_status": status,
         }

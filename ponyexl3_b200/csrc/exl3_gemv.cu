@@ -12,11 +12,15 @@ int g_gemv_smem_budget = 110 * 1024;
 static int g_fuse_x_bytes = 40 * 1024;   // fuse the input rotation when its words fit in this
 constexpr int kXsRowBytesHost = 544;
 
+static int g_cluster_cache[16][9] = {};
+
 void gemv_set_tuning(int ctas_per_sm, int smem_budget_bytes)
 {
     if (ctas_per_sm >= 1 && ctas_per_sm <= 2) g_gemv_ctas_per_sm = ctas_per_sm;
     if (smem_budget_bytes >= 32 * 1024 && smem_budget_bytes <= 226 * 1024)
         g_gemv_smem_budget = smem_budget_bytes;
+    for (auto& row : g_cluster_cache)
+        for (int& v : row) v = 0;
 }
 
 int gemv_active_clusters_probe(int cluster, int smem_bytes);   // exl3_gemv_k4.cu
@@ -25,7 +29,7 @@ int gemv_active_clusters_probe(int cluster, int smem_bytes);   // exl3_gemv_k4.c
 // is not slots / s: e.g. clusters of 7 leave a remainder in every GPC).  Cached per device.
 static int active_clusters(int s)
 {
-    static int cache[16][9] = {};
+    int (&cache)[16][9] = g_cluster_cache;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) dev = 0;
@@ -33,6 +37,7 @@ static int active_clusters(int s)
         int n = s == 1 ? device_sm_count() * g_gemv_ctas_per_sm
                        : gemv_active_clusters_probe(s, g_gemv_smem_budget);
         if (n <= 0) n = std::max(1, device_sm_count() * g_gemv_ctas_per_sm / s / 2);
+        n = std::min(n, std::max(1, device_sm_count() * g_gemv_ctas_per_sm / s));
         cache[dev][s] = n;
     }
     return cache[dev][s];

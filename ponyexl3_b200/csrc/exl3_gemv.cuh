@@ -521,7 +521,6 @@ static int launch_gemv_t(GemvArgs a, bool pdl, cudaStream_t s)
     const int stage0 = (kHeaderBytes + L::kYBytes + xs_bytes + 1023) / 1024 * 1024;
     const int stage_bytes = (XFUSED ? 0 : L::kXBoxBytes) + L::kWeightBytes;
     int budget = g_gemv_smem_budget;
-    if (g_gemv_ctas_per_sm == 1) budget = std::max(budget, 200 * 1024);
     int stages = (budget - stage0) / stage_bytes;
     if (stages < kGroups) stages = (200 * 1024 - stage0) / stage_bytes;   // one CTA per SM
     stages = std::min(stages, kMaxStages);
