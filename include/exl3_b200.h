@@ -152,6 +152,24 @@ EXL3_API int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_s
               const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
               size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
 
+/* The tensor-core GEMM over a TABLE of output tiles, for stacked MoE experts at prefill:
+ * (token, slot) pairs are sorted by expert, so each expert owns a contiguous run of rows of
+ * the rotated activations; tile t multiplies rows [row0, row_end) (at most 256) with the 256
+ * trellis columns starting at tile column tn0, scales with svh at element offset sv_off and
+ * stores ncols (128 or 256) outputs at column y_col of y rows (row + y_row_delta).
+ * `tiles` is a device array of n_tiles x {int32 row0, row_end, tn0, sv_off, y_col, ncols,
+ * y_row_delta, 0}; a slot with row0 >= row_end is skipped, so the table can be built on the
+ * device with a fixed upper bound and no host synchronisation.  Rotated row i =
+ * had(x[row_src[i]] * suh[suh_row[i]]) as in exl3_gemv_blocks.
+ * Replaces the segmented trellis GEMM of the reference, inner_mm_seg_mlx with its expert block
+ * table, ponyexl3/mlx/gemv_metal.py:1519-1741 and ponyexl3/mlx/exl3_moe.py:79-99,685-768. */
+EXL3_API int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                    const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                    const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                    const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
+                    int64_t y_row_stride, void* workspace, size_t workspace_bytes, unsigned flags,
+                    exl3_stream_t stream);
+
 /* exl3_gemv without a caller-supplied workspace, for callers that cannot allocate device
  * memory: operator slots of a serving framework or thin language bindings that are handed
  * input and output buffers but own no allocator, and decode loops where cudaMalloc is

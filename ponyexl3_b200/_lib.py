@@ -46,6 +46,9 @@ _PROTOTYPES = {
     "exl3_gemm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_size_t,
                           c_uint, c_void_p]),
+    "exl3_gemm_tiles": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64,
+                                c_void_p, c_void_p, c_int64, c_void_p, c_size_t, c_uint, c_void_p]),
     "exl3_gemv_noalloc": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int,
                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_uint,
                                   c_void_p]),

@@ -364,8 +364,57 @@ int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_stride, co
     a.status = reinterpret_cast<int*>(ws + kWsStatus);
     a.y_row_stride = y_row_stride;
     a.m = (int)rows;
+    a.xh_rows = (int)rows;
     a.t_in = (int)t_in;
     a.t_out = (int)t_out;
+    return launch_gemm(a, k, cb, xh, reinterpret_cast<const uint32_t*>(trellis), s);
+}
+
+int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                    const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                    const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                    const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
+                    int64_t y_row_stride, void* workspace, size_t workspace_bytes, unsigned flags,
+                    exl3_stream_t stream)
+{
+    (void)flags;
+    if (!x || !trellis || !y || !tiles) return EXL3_E_NULL;
+    if (k < 1 || k > 8) return EXL3_E_K;
+    if (cb < 0 || cb > 2) return EXL3_E_CODEBOOK;
+    if (t_in <= 0 || t_out_total <= 0 || t_in % 8 || t_out_total % 8) return EXL3_E_SHAPE;
+    if (t_in > (1 << 24) || t_out_total > (1 << 24)) return EXL3_E_SHAPE;
+    if (xh_rows < 1 || xh_rows > (1 << 30)) return EXL3_E_ROWS;
+    if (n_tiles < 0 || n_tiles > (1 << 24)) return EXL3_E_SHAPE;
+    const int64_t in = 16 * t_in;
+    if (x_row_stride < in) return EXL3_E_SHAPE;
+    int rc = check_dtype_align(x, x_dtype, x_row_stride);
+    if (rc) return rc;
+    if (!aligned(trellis, 16) || !aligned(y, 16) || y_row_stride % 8 || !aligned(tiles, 16))
+        return EXL3_E_ALIGN;
+    if ((suh && !aligned(suh, 8)) || (svh && !aligned(svh, 16))) return EXL3_E_ALIGN;
+    if (!workspace) return EXL3_E_WORKSPACE;
+    if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
+    if (workspace_bytes < exl3_gemm_workspace_bytes(xh_rows, in)) return EXL3_E_WORKSPACE;
+    if (n_tiles == 0) return EXL3_OK;
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    __half* xh = reinterpret_cast<__half*>(ws + kWsScratch);
+    cudaStream_t s = (cudaStream_t)stream;
+    rc = launch_hadamard(x, x_dtype, xh_rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
+                         nullptr, xh, row_src, suh_row, nullptr, false, HAD_OUT_F16, s);
+    if (rc) return rc;
+    GemmArgs a = {};
+    a.svh = reinterpret_cast<const __half*>(svh);
+    a.bias = nullptr;
+    a.y = reinterpret_cast<__half*>(y);
+    a.status = reinterpret_cast<int*>(ws + kWsStatus);
+    a.y_row_stride = y_row_stride;
+    a.tile_tab = tiles;
+    a.n_tiles_tab = (int)n_tiles;
+    a.xh_rows = (int)xh_rows;
+    a.m = (int)xh_rows;
+    a.t_in = (int)t_in;
+    a.t_out = (int)t_out_total;
     return launch_gemm(a, k, cb, xh, reinterpret_cast<const uint32_t*>(trellis), s);
 }
 

@@ -76,6 +76,35 @@ __device__ __forceinline__ void had128_regs(float (&v)[128])
             }
 }
 
+// One output tile: rows [m0, m_end) of the rotated activations against 256 trellis columns
+// starting at tile column tn0; outputs go to y rows (row + y_row_delta), columns y_col.. ;
+// svh / bias are read at sv_off.  Dense layers derive it from the tile index; grouped (MoE)
+// launches read it from a device table of 8 ints per tile, where m0 >= m_end marks an unused
+// slot that every role skips.
+struct GemmTile {
+    int m0, m_end, tn0, sv_off, y_col, ncols, y_row_delta;
+};
+__device__ __forceinline__ GemmTile gemm_tile(const GemmArgs& a, int tile)
+{
+    GemmTile t;
+    if (a.tile_tab) {
+        const int4 u = reinterpret_cast<const int4*>(a.tile_tab)[2 * tile];
+        const int4 v = reinterpret_cast<const int4*>(a.tile_tab)[2 * tile + 1];
+        t.m0 = u.x; t.m_end = u.y; t.tn0 = u.z; t.sv_off = u.w;
+        t.y_col = v.x; t.ncols = v.y; t.y_row_delta = v.z;
+    } else {
+        const int n0 = (tile % a.tiles_n) * kTileN;
+        t.m0 = (tile / a.tiles_n) * kTileM;
+        t.m_end = a.m;
+        t.tn0 = n0 / 16;
+        t.sv_off = n0;
+        t.y_col = n0;
+        t.ncols = a.t_out * 16 - n0;
+        t.y_row_delta = 0;
+    }
+    return t;
+}
+
 template <int K, int CB>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm_x,
@@ -94,7 +123,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nks = a.t_in / 4;                                // 64-wide k-steps
-    const int n_tiles = a.tiles_m * a.tiles_n;
+    const int n_tiles = a.tile_tab ? a.n_tiles_tab : a.tiles_m * a.tiles_n;
 
     if (tid == 0) {
         for (int s = 0; s < NS; s++) {
@@ -121,7 +150,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             uint32_t parity = 0;
             bool first_pass = true;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                const int m0 = (tile / a.tiles_n) * kTileM, tn0 = (tile % a.tiles_n) * 16;
+                const GemmTile ti = gemm_tile(a, tile);
+                if (ti.m0 >= ti.m_end) continue;
+                const int m0 = ti.m0, tn0 = ti.tn0;
                 for (int ks = 0; ks < nks; ks++) {
                     if (!first_pass && !mbar_wait(smem_u32(&empty[s]), parity ^ 1u)) {
                         atomicOr(a.status, ST_TC_TIMEOUT);
@@ -145,6 +176,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             uint32_t parity = 0, tile_parity = 0;
             bool first_tile = true;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                {
+                    const GemmTile ti = gemm_tile(a, tile);
+                    if (ti.m0 >= ti.m_end) continue;
+                }
                 if (!first_tile) {   // the epilogue of the previous tile must have drained D
                     if (!mbar_wait(smem_u32(tmem_empty), tile_parity ^ 1u)) {
                         atomicOr(a.status, ST_TC_TIMEOUT);
@@ -188,7 +223,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int s = 0;
         uint32_t parity = 0, tile_parity = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-            const int m0 = (tile / a.tiles_n) * kTileM, n0 = (tile % a.tiles_n) * kTileN;
+            const GemmTile ti = gemm_tile(a, tile);
+            if (ti.m0 >= ti.m_end) continue;
+            const int m0 = ti.m0;
             for (int ks = 0; ks < nks; ks++) {
                 // all lanes take the same decision: the tensor-memory loads below are warp-wide
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&a_full[s]), parity))) {
@@ -234,8 +271,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tile_parity ^= 1u;
             tc_fence_after_sync();
             const int quarter = warp & 3, chalf = dw >> 2;
-            const int col0 = n0 + 128 * chalf;
-            if (col0 < a.t_out * 16) {
+            const int col0 = ti.y_col + 128 * chalf, sv0 = ti.sv_off + 128 * chalf;
+            if (128 * chalf < ti.ncols) {
 #pragma unroll 1
                 for (int acc = 0; acc < 2; acc++) {
                     const int row = m0 + 128 * acc + 32 * quarter + lane;
@@ -250,15 +287,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         for (int i = 0; i < 32; i++) v[32 * c + i] = __half2float(__float2half_rn(t32[i]));
                     }
                     had128_regs(v);
-                    if (row < a.m) {
-                        __half* yp = a.y + (int64_t)row * a.y_row_stride + col0;
+                    if (row < ti.m_end) {
+                        __half* yp = a.y + (int64_t)(row + ti.y_row_delta) * a.y_row_stride + col0;
 #pragma unroll
                         for (int c = 0; c < 16; c++) {
                             float o[8];
 #pragma unroll
                             for (int i = 0; i < 8; i++) o[i] = v[8 * c + i] * EXL3_HAD_SCALE;
                             if (a.svh) {
-                                const uint4 sv = *reinterpret_cast<const uint4*>(a.svh + col0 + 8 * c);
+                                const uint4 sv = *reinterpret_cast<const uint4*>(a.svh + sv0 + 8 * c);
                                 const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
                                 for (int i = 0; i < 4; i++) {
@@ -271,7 +308,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                             for (int i = 0; i < 4; i++) h[i] = __floats2half2_rn(o[2 * i], o[2 * i + 1]);
                             if (a.bias) {
-                                const uint4 bv = *reinterpret_cast<const uint4*>(a.bias + col0 + 8 * c);
+                                const uint4 bv = *reinterpret_cast<const uint4*>(a.bias + sv0 + 8 * c);
                                 const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
                                 for (int i = 0; i < 4; i++) h[i] = __hadd2(h[i], u32_as_h2(bw[i]));
@@ -316,7 +353,7 @@ static int launch_gemm_t(GemmArgs a, const __half* xh, const uint32_t* trellis, 
     CUtensorMap tm_x, tm_w;
     {
         const uint64_t in = (uint64_t)a.t_in * 16;
-        const uint64_t xdims[2] = {in, (uint64_t)a.m};
+        const uint64_t xdims[2] = {in, (uint64_t)a.xh_rows};
         const uint64_t xstrides[1] = {in * 2};
         const uint32_t xbox[2] = {(uint32_t)kStepK, 128u};
         int rc = make_tensor_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, xh, xdims, xstrides, xbox,
@@ -332,7 +369,7 @@ static int launch_gemm_t(GemmArgs a, const __half* xh, const uint32_t* trellis, 
     a.tiles_m = (a.m + kTileM - 1) / kTileM;
     a.tiles_n = (a.t_out * 16 + kTileN - 1) / kTileN;
     a.cb_xor = 0x3B603B60u;
-    const int grid = std::min(a.tiles_m * a.tiles_n, device_sm_count());
+    const int grid = std::min(a.tile_tab ? a.n_tiles_tab : a.tiles_m * a.tiles_n, device_sm_count());
     gemm_kernel<K, CB><<<grid, kGemmThreads, L::kSmemBytes, s>>>(a, tm_x, tm_w);
     return check_launch();
 }

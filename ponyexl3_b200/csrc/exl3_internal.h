@@ -84,6 +84,9 @@ struct GemmArgs {
     __half* y;
     int* status;
     int64_t y_row_stride;
+    const int32_t* tile_tab;  // grouped launches: device table of 8 ints per tile, else NULL
+    int n_tiles_tab;          // slots in tile_tab
+    int xh_rows;              // rows of the rotated-activation matrix
     int m;                    // rows (tokens)
     int t_in, t_out;          // tiles
     int tiles_m, tiles_n;

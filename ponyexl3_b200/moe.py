@@ -12,7 +12,8 @@ mlx_lm's SwitchGLU; routing and the weighted sum stay in the block.
 Decode-class calls (few tokens) run two streamed GEMVs over block tables built on the device
 from the routing indices — every (token, slot) pair is its own one-row problem against its
 expert's column range (the reference's mapped GEMV, exl3_moe.py:634-683).  Prefill-class
-calls sort the pairs by expert and run the tensor-core GEMM per expert segment.
+calls sort the pairs by expert and run the tensor-core GEMM over a table of expert tiles
+(the reference's segmented trellis GEMM, exl3_moe.py:685-768).
 """
 
 from __future__ import annotations
@@ -107,37 +108,76 @@ class EXL3SwitchGLU(torch.nn.Module):
                         svh=self._dn_svh, bias=None, y=y, pdl=self.pdl)
         return y.view(R, kk, D)
 
-    # ---- prefill: pairs sorted by expert, one GEMM per expert segment ----------------------------
+    # ---- prefill: pairs sorted by expert, tensor-core GEMM over an expert tile table ----------
+    @staticmethod
+    def _segments(sidx: torch.Tensor, E: int, n_pairs: int):
+        """Row tiles of <= 256 sorted pairs that never straddle two experts, built on the device
+        with a fixed upper bound of slots (the reference's block table, exl3_moe.py:79-99):
+        expert, first row and end row of every slot; unused slots have row0 == row_end."""
+        dev = sidx.device
+        mt = n_pairs // 256 + E
+        counts = torch.bincount(sidx, minlength=E)
+        nblk = (counts + 255) // 256
+        blk_end = torch.cumsum(nblk, 0)
+        slot = torch.arange(mt, device=dev)
+        blk_e = torch.clamp(torch.searchsorted(blk_end, slot, right=True), max=E - 1)
+        valid = slot < blk_end[-1]
+        seg_start = torch.cumsum(counts, 0) - counts
+        local = slot - (blk_end - nblk)[blk_e]
+        row0 = seg_start[blk_e] + local * 256
+        row_end = torch.minimum(row0 + 256, seg_start[blk_e] + counts[blk_e])
+        row0 = torch.where(valid, row0, torch.zeros_like(row0))
+        row_end = torch.where(valid, row_end, torch.zeros_like(row_end))
+        return blk_e.to(torch.int32), row0.to(torch.int32), row_end.to(torch.int32)
+
+    @staticmethod
+    def _tiles(blk_e, row0, row_end, *, cols, tn_base, tiles_per_e, sv_base, sv_per_e, y_col0, row_shift):
+        """Tile table of one projection: every row tile x every 256-column tile of its expert."""
+        dev = blk_e.device
+        ct = (cols + 255) // 256
+        j = torch.arange(ct, device=dev, dtype=torch.int32).view(1, ct)
+        e = blk_e.view(-1, 1)
+        z = torch.zeros_like(e)
+        tab = torch.stack([
+            (row0.view(-1, 1) + row_shift) + z * j, (row_end.view(-1, 1) + row_shift) + z * j,
+            tn_base + e * tiles_per_e + 16 * j, sv_base + e * sv_per_e + 256 * j,
+            y_col0 + 256 * j + z, torch.clamp(cols - 256 * j, max=256) + z,
+            z * j - row_shift, z * j], dim=-1)
+        # slots that are unused must stay unused after the row shift
+        empty = (row0 >= row_end).view(-1, 1, 1)
+        tab = torch.where(empty & (torch.arange(8, device=dev).view(1, 1, 8) < 2), torch.zeros_like(tab), tab)
+        return tab.reshape(-1, 8).to(torch.int32).contiguous()
+
     def _prefill(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
         E, D, H = self.num_experts, self.input_dims, self.hidden_dims
         R, kk = indices.shape
+        n = R * kk
+        dev = x2d.device
         flat = indices.reshape(-1).to(torch.int64)
         order = torch.argsort(flat, stable=True)
         sidx = flat[order]
-        tok = torch.div(order, kk, rounding_mode="floor")
-        counts = torch.bincount(sidx, minlength=E).cpu().tolist()       # segment sizes (host)
-        xs = x2d[tok]
-        out = torch.empty((R * kk, D), dtype=torch.float16, device=x2d.device)
-        gu_suh = self._gu_suh.view(E, 2, D)
-        gu_svh = self._gu_svh.view(E, 2 * H)
-        dn_svh = self._dn_svh.view(E, D)
-        gt, dt = H // 16, D // 16
-        r0 = 0
-        for e, c in enumerate(counts):
-            if c == 0:
-                continue
-            xe = xs[r0:r0 + c]
-            fwd = ops.gemm if c > 16 else ops.gemv
-            g = fwd(xe, self._gu_trellis[:, e * gt:(e + 1) * gt].contiguous(), self.k, self.cb,
-                    gu_suh[e, 0], gu_svh[e, :H], None)
-            u = fwd(xe, self._gu_trellis[:, (E + e) * gt:(E + e + 1) * gt].contiguous(), self.k, self.cb,
-                    gu_suh[e, 1], gu_svh[e, H:], None)
-            h = glu(g, u, self.activation)
-            fwd(h, self._dn_trellis[:, e * dt:(e + 1) * dt].contiguous(), self.k, self.cb,
-                self._dn_suh[e], dn_svh[e], None, out=out[r0:r0 + c])
-            r0 += c
+        tok = torch.div(order, kk, rounding_mode="floor").to(torch.int32)
+        blk_e, row0, row_end = self._segments(sidx, E, n)
+        s32 = sidx.to(torch.int32)
+
+        # gate and up in one launch: rotated rows [0, n) use the gate signs, [n, 2n) the up signs
+        t_g = self._tiles(blk_e, row0, row_end, cols=H, tn_base=0, tiles_per_e=H // 16, sv_base=0,
+                          sv_per_e=2 * H, y_col0=0, row_shift=0)
+        t_u = self._tiles(blk_e, row0, row_end, cols=H, tn_base=E * (H // 16), tiles_per_e=H // 16,
+                          sv_base=H, sv_per_e=2 * H, y_col0=H, row_shift=n)
+        ygu = torch.empty((n, 2 * H), dtype=torch.float16, device=dev)
+        ops.gemm_tiles(x2d, xh_rows=2 * n, row_src=torch.cat([tok, tok]).contiguous(), suh=self._gu_suh,
+                       suh_row=torch.cat([2 * s32, 2 * s32 + 1]).contiguous(), trellis=self._gu_trellis,
+                       k=self.k, cb=self.cb, tiles=torch.cat([t_g, t_u]), svh=self._gu_svh, y=ygu)
+        h = glu(ygu[:, :H], ygu[:, H:], self.activation)
+
+        t_d = self._tiles(blk_e, row0, row_end, cols=D, tn_base=0, tiles_per_e=D // 16, sv_base=0,
+                          sv_per_e=D, y_col0=0, row_shift=0)
+        out = torch.empty((n, D), dtype=torch.float16, device=dev)
+        ops.gemm_tiles(h, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=s32.contiguous(),
+                       trellis=self._dn_trellis, k=self.k, cb=self.cb, tiles=t_d, svh=self._dn_svh, y=out)
         inv = torch.empty_like(order)
-        inv[order] = torch.arange(order.numel(), device=order.device)
+        inv[order] = torch.arange(n, device=dev)
         return out[inv].view(R, kk, D)
 
     @torch.no_grad()

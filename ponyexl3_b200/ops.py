@@ -230,3 +230,28 @@ def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None
         (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0),
         _stream(x2d.device)), "exl3_gemv_blocks")
     return y
+
+
+def gemm_tiles(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None,
+               suh: torch.Tensor | None, suh_row: torch.Tensor | None, trellis: torch.Tensor, k: int,
+               cb: int, tiles: torch.Tensor, svh: torch.Tensor | None, y: torch.Tensor) -> torch.Tensor:
+    """Tensor-core GEMM over a tile table (see exl3_gemm_tiles in the header).  `tiles` is an
+    int32 CUDA tensor (n_tiles, 8); `y` (rows, cols) fp16 is written in place."""
+    _need_cuda(x2d, "x")
+    t_in, t_out_total, _ = trellis.shape
+    if x2d.shape[1] != t_in * 16:
+        raise ValueError(f"x has {x2d.shape[1]} features, layer expects {t_in * 16}")
+    if tiles.dtype != torch.int32 or tiles.ndim != 2 or tiles.shape[1] != 8:
+        raise ValueError("tiles must be an int32 tensor of shape (n_tiles, 8)")
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    tiles = tiles.contiguous()
+    lib = _lib.load()
+    ws = Workspace.get_bytes(x2d.device, int(lib.exl3_gemm_workspace_bytes(xh_rows, t_in * 16)))
+    ptr = lambda t: None if t is None else t.data_ptr()
+    _lib.check(lib.exl3_gemm_tiles(
+        x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),
+        ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), tiles.data_ptr(),
+        tiles.shape[0], ptr(svh), y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes, 0,
+        _stream(x2d.device)), "exl3_gemm_tiles")
+    return y

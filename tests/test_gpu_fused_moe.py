@@ -134,3 +134,20 @@ def test_config4_moe_block_one_token(cuda, oracle):
     blk = EXL3MoEBlock(gate_w, sw, kk)
     out = blk(torch.from_numpy(x).cuda())
     assert out.shape == (1, D) and torch.isfinite(out.float()).all()
+
+
+def test_config4_prefill_tile_table(cuda, oracle):
+    """Config-4 expert dims with 128 tokens x top-8 = 1024 sorted pairs over 256 experts: most
+    row tiles are ragged and many table slots stay unused."""
+    E, D, H, kk, k = 256, 2048, 512, 8, 4
+    w = _experts(E, D, H, k, seed=4100)
+    sw = _switch(w, k, 0)
+    rng = np.random.default_rng(4101)
+    T = 128
+    x = (rng.standard_normal((T, D)) * 0.02).astype(np.float16)
+    idx = np.stack([rng.choice(E, size=kk, replace=False) for _ in range(T)]).astype(np.int64)
+    y = sw(torch.from_numpy(x).cuda().view(1, T, D), torch.from_numpy(idx).cuda().view(1, T, kk))
+    from ponyexl3_b200 import ops
+    assert ops.Workspace.get(torch.device("cuda"), 1, 128).status() == 0
+    want = oracle.switch_glu(x, idx, **w, k=k, cb=0)
+    assert rel_err(y.cpu().numpy().reshape(T, kk, D), want) <= 2e-3
