@@ -397,6 +397,34 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_profile_case(case: str):
+    """Small fixed cases for `ncu` captures (a few launches, a few GB at most on the device):
+    gemv = four batch-1 GEMVs 5120->17408 K=4 on distinct layers; gemm = three prefill GEMMs
+    8192 x 5120 -> 5120 K=4 with bf16 activations."""
+    import torch
+    from ponyexl3_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    if case == "gemv":
+        inf, outf, rows, n = 5120, 17408, 1, 4
+    else:
+        inf, outf, rows, n = 5120, 5120, 8192, 1
+    trs = [torch.randint(-32768, 32767, (inf // 16, outf // 16, 16 * K_BITS), dtype=torch.int16,
+                         device=dev, generator=g) for _ in range(n)]
+    suh = (torch.randint(0, 2, (inf,), device=dev, generator=g) * 2 - 1).to(torch.float16)
+    svh = (torch.randint(0, 2, (outf,), device=dev, generator=g) * 2 - 1).to(torch.float16)
+    x = torch.randn((rows, inf), device=dev, generator=g)
+    x = x.to(torch.float16) if case == "gemv" else x.to(torch.bfloat16)
+    for i in range(4 if case == "gemv" else 3):
+        fn = ops.gemv if case == "gemv" else ops.gemm
+        y = fn(x, trs[i % n], K_BITS, CB, suh, svh, None)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": case, "mean_abs_y": float(y.float().abs().mean())}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -406,7 +434,12 @@ def main():
     ap.add_argument("--ring", type=int, default=16, help="layer sets per step")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--profile-case", choices=["gemv", "gemm"], default=None,
+                    help="run one small case for an ncu capture and exit")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
