@@ -16,6 +16,9 @@ _LAZY = {
     "FusedEXL3Sibling": ".fused",
     "EXL3SwitchGLU": ".moe",
     "EXL3MoEBlock": ".moe",
+    "EXL3Checkpoint": ".loader",
+    "load_exl3_layer": ".loader",
+    "list_exl3_layers": ".loader",
 }
 
 
