@@ -31,9 +31,13 @@ sys.path.insert(0, str(ROOT))
 
 SHAPES = [(5120, 17408), (17408, 5120), (5120, 5120)]
 K_BITS, CB, ROWS = 4, 0, 1
+CB_NAMES = {0: "3INST", 1: "MCG", 2: "MUL1"}
 METRIC = "exl3_gemv_packed_weight_bandwidth"
 UNIT = "GB/s"
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum over packed weight bytes, from the ncu capture of
+# the K=4 batch-1 GEMV 5120 -> 17408 (profiles/gemv_k4_b1_5120x17408.md)
+DRAM_TRAFFIC_RATIO = 1.0027
 
 
 def packed_bytes(shape, k=K_BITS):
@@ -378,7 +382,12 @@ def run_gpu(args):
             },
             "roofline": {
                 "bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
-                "frac": per_gpu / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                "frac": per_gpu / peak, "traffic": DRAM_TRAFFIC_RATIO * step_bytes_global / world / n_gemv,
+                "traffic_unit": "bytes per launch (dram read + write)",
+                "traffic_note": "ncu capture of the 5120x17408 launch: 44.68 MB read + 2.3 KB written for "
+                                "44.56 MB of packed weights (ratio 1.0027); scaled by packed bytes to the "
+                                "average launch of this step",
+                "peak_kind": f"of {peak_kind}",
                 "kernel": "exl3::gemv_kernel<4,0,1>",
                 "note": "achieved = packed bytes per launch / (step time / GEMV launches); both "
                         "rotations run inside the GEMV kernel",
@@ -395,6 +404,222 @@ def run_gpu(args):
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def run_decode(args):
+    """BASELINE.json configs[4]: one greedy decode step of the synthetic 64-layer dense model
+    (all linears EXL3, K in {4,5}, KV context 8192) at --rows new positions, tensor parallel by
+    output tile over the launched ranks.  A step = one forward + arg-max, captured in a CUDA
+    graph; value = rows / step time."""
+    import numpy as np
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import datetime
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+    from ponyexl3_b200 import ops
+    from ponyexl3_b200.dense_step import DenseConfig, SyntheticDenseDecoder
+
+    cfg = DenseConfig(layers=args.layers, max_rows=max(16, args.rows))
+    dec = SyntheticDenseDecoder(cfg, dev, seed=5000)
+    rows = args.rows
+    tok_in = torch.randint(0, cfg.vocab, (rows,), device=dev, generator=torch.Generator(device=dev).manual_seed(5))
+    stream = torch.cuda.Stream(device=dev)
+    graph = None
+    with torch.cuda.stream(stream):
+        tok_out = dec.step(tok_in)
+        stream.synchronize()
+        if not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                tok_out = dec.step(tok_in)
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+            return tok_out
+        return dec.step(tok_in)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            run_step()
+        barrier()
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            run_step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        # end to end: token ids come from pinned host memory, the chosen tokens go back to it
+        h_tok = tok_in.cpu().pin_memory()
+        h_out = torch.empty((rows,), dtype=torch.int64).pin_memory()
+        e2e_steps = max(3, min(args.steps, 20))
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            tok_in.copy_(h_tok, non_blocking=True)
+            out = run_step()
+            h_out.copy_(out, non_blocking=True)
+            stream.synchronize()
+            h_tok.copy_(h_out % cfg.vocab)
+        barrier()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([ms, e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0].item()), float(t[1].item())
+    status = ops.Workspace.get(dev, 1, 128).status()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        from oracle import exl3_oracle as oracle
+        oracle.lib()
+        cores = oracle.host_cores()
+        oracle.set_threads(cores)
+        rng = np.random.default_rng(5000)
+        d, i = cfg.hidden, cfg.intermediate
+        slots = [(d, (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim), (d, d), (d, 2 * i), (i, d)]
+        t_layer = 0.0
+        for (inf, outf) in slots:
+            tr = rng.integers(0, 65536, size=(inf // 16, outf // 16, 64), dtype=np.uint16)
+            sg = np.ones(inf, dtype=np.float16)
+            sv = np.ones(outf, dtype=np.float16)
+            x = rng.standard_normal((rows, inf)).astype(np.float16)
+            t0 = time.perf_counter()
+            oracle.linear_forward(x, tr, 4, 0, sg, sv)
+            t_layer += time.perf_counter() - t0
+        weights_layer = sum(a * b for a, b in slots)
+        est = t_layer * (cfg.layers * weights_layer + d * cfg.vocab) / weights_layer
+        cpu = {"value": rows / est, "unit": "tok/s", "cores": cores, "kind": "port",
+               "sample": f"the four linear slots of ONE layer at K=4 through the C oracle ({t_layer:.2f} s), "
+                         f"scaled by weight count to {cfg.layers} layers + head; attention and norms not "
+                         f"included (they favour the CPU figure)"}
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        step_s = ms * 1e-3 / args.steps
+        bytes_gpu = dec.packed_local + dec.kv_bytes_local
+        line = {
+            "metric": "decode_tokens_per_s", "value": rows / step_s, "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": 1e3 * step_s,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {
+                "workload": f"configs[4]: greedy decode step, {cfg.layers} layers, hidden {cfg.hidden}, "
+                            f"MLP {cfg.intermediate}, {cfg.q_heads}q/{cfg.kv_heads}kv heads x {cfg.head_dim}, "
+                            f"vocab {cfg.vocab}, KV context {cfg.context}, rows {rows}",
+                "rows": rows, "bits": "K in {4,5}, mean %.3f bpw" % (sum(dec.ks) / len(dec.ks)),
+                "packed_bytes_per_gpu": dec.packed_local, "kv_bytes_per_gpu": dec.kv_bytes_local,
+                "l2": "weights + KV per GPU per step far larger than the 126 MB L2",
+                "launch": "cuda_graph" if graph is not None else "eager",
+                "parallelism": f"tp{world} by output tile, heads sharded, 4 all-gathers per layer"
+                               if world > 1 else "single GPU",
+                "glue": "RMSNorm, RoPE, attention (SDPA), SwiGLU, residual adds are PyTorch ops",
+            },
+            "roofline": {"bound": "hbm", "achieved": bytes_gpu / step_s / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": bytes_gpu / step_s / 1e9 / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "note": "whole step: packed weights + KV cache bytes per GPU over the step time"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": rows / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8 * rows,
+                    "d2h_bytes_per_step": 8 * rows, "ms_per_step": 1e3 * e2e_s,
+                    "api": "SyntheticDenseDecoder.step, token ids from and to pinned host memory"},
+            "gpu_launches": (cfg.layers * 6 + 1) * args.steps,
+            "clocks": clocks, "kernel_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_sweep(args):
+    """BASELINE.json configs[1] in full: rows x K x codebook x shape, one graph-captured train
+    of launches over distinct layers (more packed bytes than L2) per case.  Prints one JSON
+    line per case and, with --sweep-out, writes a markdown table."""
+    import torch
+    from ponyexl3_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    peak, peak_kind = measured_peaks()
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2000)
+    rows_list = [int(r) for r in args.sweep_rows.split(",")]
+    ks = [int(k) for k in args.sweep_k.split(",")]
+    cbs = [int(c) for c in args.sweep_cb.split(",")]
+    stream = torch.cuda.Stream(device=dev)
+    results = []
+    for (inf, outf) in SHAPES:
+        suh = (torch.randint(0, 2, (inf,), device=dev, generator=gen) * 2 - 1).to(torch.float16)
+        svh = (torch.randint(0, 2, (outf,), device=dev, generator=gen) * 2 - 1).to(torch.float16)
+        for k in ks:
+            per = inf * outf * k // 8
+            n = max(3, min(96, int(2.5 * L2_BYTES // per) + 1))       # distinct layers per train
+            trs = [torch.randint(-32768, 32767, (inf // 16, outf // 16, 16 * k), dtype=torch.int16,
+                                 device=dev, generator=gen) for _ in range(n)]
+            for rows in rows_list:
+                x = torch.randn((rows, inf), device=dev, generator=gen).to(torch.float16)
+                y = torch.empty((rows, outf), dtype=torch.float16, device=dev)
+                for cb in cbs:
+                    with torch.cuda.stream(stream):
+                        ops.gemv(x, trs[0], k, cb, suh, svh, None, pdl=True, out=y)
+                        stream.synchronize()
+                        g = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(g, stream=stream):
+                            for t in trs:
+                                ops.gemv(x, t, k, cb, suh, svh, None, pdl=True, out=y)
+                        for _ in range(3):
+                            g.replay()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        stream.synchronize()
+                        e0.record(stream)
+                        for _ in range(args.sweep_iters):
+                            g.replay()
+                        e1.record(stream)
+                        stream.synchronize()
+                    us = 1e3 * e0.elapsed_time(e1) / args.sweep_iters / n
+                    gbs = per / (us * 1e-6) / 1e9
+                    r = {"shape": f"{inf}x{outf}", "k": k, "cb": CB_NAMES[cb], "rows": rows,
+                         "us_per_launch": round(us, 2), "packed_gbs": round(gbs, 1),
+                         "frac_hbm": round(gbs / peak, 4), "gweights_s": round(inf * outf / us / 1e3, 1),
+                         "other_bytes": 2 * rows * (inf + outf) + 2 * (inf + outf), "layers_in_train": n}
+                    print(json.dumps(r), flush=True)
+                    results.append(r)
+                    del g
+            del trs
+            torch.cuda.empty_cache()
+    if args.sweep_out:
+        lines = [f"Peak: {peak:.1f} GB/s ({peak_kind}).  Cells: packed-weight GB/s (fraction of peak), "
+                 f"3INST / MCG / MUL1.", ""]
+        for (inf, outf) in SHAPES:
+            lines += [f"### {inf} -> {outf}", "", "| K | " + " | ".join(f"rows={r}" for r in rows_list) + " |",
+                      "|---|" + "---|" * len(rows_list)]
+            for k in ks:
+                cells = []
+                for rows in rows_list:
+                    v = [r for r in results if r["shape"] == f"{inf}x{outf}" and r["k"] == k and r["rows"] == rows]
+                    cells.append(" / ".join(f"{r['packed_gbs']:.0f} ({r['frac_hbm']:.2f})" for r in v))
+                lines.append(f"| {k} | " + " | ".join(cells) + " |")
+            lines.append("")
+        Path(args.sweep_out).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.sweep_out).write_text("\n".join(lines))
 
 
 def run_profile_case(case: str):
@@ -436,12 +661,28 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--profile-case", choices=["gemv", "gemm"], default=None,
                     help="run one small case for an ncu capture and exit")
+    ap.add_argument("--sweep", action="store_true",
+                    help="rows x K x codebook x shape GEMV sweep (one JSON line per case) and exit")
+    ap.add_argument("--sweep-rows", default="1,2,4,8,16")
+    ap.add_argument("--sweep-k", default="1,2,3,4,5,6,7,8")
+    ap.add_argument("--sweep-cb", default="0,1,2")
+    ap.add_argument("--sweep-iters", type=int, default=5)
+    ap.add_argument("--sweep-out", default=None, help="write a markdown table of the sweep here")
+    ap.add_argument("--workload", choices=["gemv", "decode"], default="gemv",
+                    help="gemv = the headline batch-1 GEMV ring; decode = the 64-layer decode step")
+    ap.add_argument("--rows", type=int, default=1, help="decode workload: new positions per step (1 or 16)")
+    ap.add_argument("--layers", type=int, default=64, help="decode workload: transformer layers")
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.profile_case:
         run_profile_case(args.profile_case)
         return
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_gpu(args)
 

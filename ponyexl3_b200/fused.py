@@ -64,8 +64,40 @@ class FusedEXL3Group(torch.nn.Module):
         self._cache_out: tuple[torch.Tensor, ...] | None = None
         self.pdl = False
 
+    @classmethod
+    def from_device_tensors(cls, *, trellis: torch.Tensor, k: int, cb: int, suh_stack: torch.Tensor,
+                            svh_cat: torch.Tensor, out_features: list[int],
+                            keys: list[str] | None = None) -> "FusedEXL3Group":
+        """Build the group around tensors already on the device (a shard, or synthetic weights):
+        trellis (in/16, sum(out)/16, 16k) int16 with the members side by side, suh_stack
+        (members, in) fp16, svh_cat (sum(out),) fp16."""
+        total = sum(out_features)
+        if trellis.ndim != 3 or trellis.shape[2] != 16 * k or trellis.shape[1] * 16 != total:
+            raise ValueError(f"trellis shape {tuple(trellis.shape)} does not fit K={k}, out={total}")
+        if (trellis.shape[0] * 16) % 128 or any(n % 128 for n in out_features):
+            raise ValueError("in features and member widths must be multiples of 128")
+        if tuple(suh_stack.shape) != (len(out_features), trellis.shape[0] * 16) or svh_cat.numel() != total:
+            raise ValueError("suh_stack / svh_cat do not match the members")
+        g = cls.__new__(cls)
+        torch.nn.Module.__init__(g)
+        g._keys = list(keys) if keys else [f"member{i}" for i in range(len(out_features))]
+        g.k, g.cb = int(k), int(cb)
+        g.in_features = trellis.shape[0] * 16
+        g._out_features = [int(n) for n in out_features]
+        g._trellis, g._suh_stack, g._svh_cat = trellis.contiguous(), suh_stack.contiguous(), svh_cat
+        g._block_sub = np.repeat(np.arange(len(out_features)), [n // 128 for n in out_features])
+        g._offsets = np.concatenate([[0], np.cumsum(g._out_features)]).astype(np.int64)
+        g._tables = {}
+        g._cache_x = g._cache_out = None
+        g.pdl = False
+        return g
+
     def extra_repr(self) -> str:
         return f"members={self._keys}, k={self.k}"
+
+    @property
+    def packed_bytes(self) -> int:
+        return self.in_features * int(self._offsets[-1]) * self.k // 8
 
     def _table(self, rows: int, device: torch.device):
         """Block table and rotation indices for `rows` activation rows (cached per row count):
