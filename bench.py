@@ -577,6 +577,7 @@ def run_sweep(args):
             for rows in rows_list:
                 x = torch.randn((rows, inf), device=dev, generator=gen).to(torch.float16)
                 y = torch.empty((rows, outf), dtype=torch.float16, device=dev)
+                stream.wait_stream(torch.cuda.current_stream(dev))     # inputs are written before use
                 for cb in cbs:
                     with torch.cuda.stream(stream):
                         ops.gemv(x, trs[0], k, cb, suh, svh, None, pdl=True, out=y)
@@ -594,6 +595,9 @@ def run_sweep(args):
                             g.replay()
                         e1.record(stream)
                         stream.synchronize()
+                    status = ops.Workspace.get(dev, rows, inf).status()
+                    if status:
+                        raise SystemExit(f"kernel status {status} at {inf}x{outf} K={k} cb={cb} rows={rows}")
                     us = 1e3 * e0.elapsed_time(e1) / args.sweep_iters / n
                     gbs = per / (us * 1e-6) / 1e9
                     r = {"shape": f"{inf}x{outf}", "k": k, "cb": CB_NAMES[cb], "rows": rows,

@@ -16,6 +16,7 @@ enum : int {
     ST_WAIT_FULL_TIMEOUT = 1,    // a consumer gave up waiting for a staged item
     ST_WAIT_EMPTY_TIMEOUT = 2,   // the producer gave up waiting for a free stage
     ST_TC_TIMEOUT = 4,           // a tensor-core pipeline wait gave up
+    ST_BAD_LAUNCH = 8,           // a kernel found its launch (shared memory, cluster) not as planned
 };
 
 // ---- codebooks: exact fp16 arithmetic -------------------------------------------------

@@ -79,6 +79,18 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
     return r;
 }
+__device__ __forceinline__ uint32_t cluster_nctaid_x()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t dynamic_smem_bytes()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(r));
+    return r;
+}
 __device__ __forceinline__ void cluster_sync_all()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
@@ -172,6 +184,14 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
     const int ns = a.stages;
     const int xbox = XFUSED ? 0 : L::kXBoxBytes;
     const int stage_bytes = xbox + L::kWeightBytes;
+
+    // The launch must match the plan the host made: every thread of every CTA takes the same
+    // branch here, so a mismatch ends the grid before any barrier or remote access.
+    if (dynamic_smem_bytes() < (uint32_t)(a.stage0_off + ns * stage_bytes) || ns < kGroups || ns > kMaxStages ||
+        (S > 1 && cluster_nctaid_x() != (uint32_t)S) || (gridDim.x % (unsigned)S) != 0) {
+        if (tid == 0) atomicOr(a.status, ST_BAD_LAUNCH);
+        return;
+    }
 
     if (tid == 0) {
         for (int s = 0; s < ns; s++) {
@@ -484,6 +504,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         if (!mbar_wait_cluster(smem_u32(red_done), red_parity ^ 1u) && lane == 0)
             atomicOr(a.status, ST_WAIT_FULL_TIMEOUT);
     }
+    // No CTA of a cluster leaves while another may still arrive on its barriers or read its
+    // partial sums — also when a bounded wait above gave up.  (The producer lane has issued
+    // all its copies long before; threads that have exited do not take part.)
+    if (S > 1) cluster_sync_all();
 #ifdef EXL3_PROFILE
     if (a.prof && lane == 0) {
         long long* p = a.prof + ((size_t)blockIdx.x * kConsumerWarps + warp) * 8;
