@@ -260,7 +260,10 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
     a.x_dtype = x_dtype;
     a.x_fused = x_fused ? 1 : 0;
 #ifdef EXL3_PROFILE
-    a.prof = reinterpret_cast<long long*>(ws + kWsScratch);   // timing builds reuse the scratch area
+    {   // timing builds reuse the scratch area; consecutive launches alternate between two slots
+        static int prof_launch = 0;
+        a.prof = reinterpret_cast<long long*>(ws + kWsScratch) + (size_t)(prof_launch++ & 1) * 400 * 16 * 16;
+    }
 #endif
     return launch_gemv(a, k, cb, pdl, s);
 }

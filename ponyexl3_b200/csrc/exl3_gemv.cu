@@ -45,11 +45,14 @@ static int active_clusters(int s)
 
 // k-split S and grid for a layer.  Time is proportional to (waves of clusters) x (k-blocks
 // per CTA); pick the S that minimises it, preferring the smaller S on ties.
-void gemv_choose_split(int ncb, int nkb, int* ksplit, int* grid)
+// The leader keeps (S - 1) x rows x 128 floats of landing slots for the others' partial sums;
+// S is capped so that they stay under 24 KiB.
+void gemv_choose_split(int ncb, int nkb, int rows, int* ksplit, int* grid)
 {
     int best_s = 1, best_clusters = 1;
     long best_t = -1;
-    for (int s = 1; s <= std::min(8, nkb); s++) {
+    const int s_max = std::min(std::min(8, nkb), 1 + 24576 / (rows * 512));
+    for (int s = 1; s <= s_max; s++) {
         const int clusters = std::min(ncb, active_clusters(s));
         const long waves = (ncb + clusters - 1) / clusters;
         const long t = waves * ((nkb + s - 1) / s) * 16 + s;   // + s: cost of gathering s partial sums
@@ -67,7 +70,7 @@ bool gemv_x_is_fused(int rows, int t_in, int ncb)
 {
     if (rows > 8) return false;
     int s, grid;
-    gemv_choose_split(ncb, t_in >> 3, &s, &grid);
+    gemv_choose_split(ncb, t_in >> 3, rows, &s, &grid);
     const int nkb = t_in >> 3;
     const int klen = (nkb + s - 1) / s;
     return (klen * rows + 1) * kXsRowBytesHost <= g_fuse_x_bytes;

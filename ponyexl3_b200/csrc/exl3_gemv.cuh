@@ -6,10 +6,11 @@
 // so every CTA streams "items" of 8x8 packed tiles (one k-block of one column block,
 // 2*K KiB) and keeps its slice of the rotated activations for its whole life.  S is chosen
 // on the host so that (column blocks x S) fills the two CTA slots of every SM.  When a
-// block is finished the CTAs' fp32 partial sums meet in the leader CTA through distributed
-// shared memory (remote mbarrier arrive + ld.shared::cluster, a few hundred ns) instead
-// of through global memory, and the leader rounds to fp16 as the reference does, applies
-// the output Hadamard-128, svh and bias, and stores the block.
+// block is finished the other CTAs PUSH their fp32 partial sums into landing slots in the
+// leader's shared memory (st.shared::cluster, then one remote mbarrier arrive) and, after
+// their last block, leave at once; the leader adds the slots in rank order, rounds to fp16
+// as the reference does, applies the output Hadamard-128, svh and bias, and stores the
+// block.  Nothing goes through global memory and nobody reads a remote CTA's memory.
 //
 // Inside a CTA one producer lane feeds a shared-memory ring with TMA tensor copies
 // (completion counted on mbarriers): ONE 3-D box per item.  Weight copies of the first
@@ -91,9 +92,33 @@ __device__ __forceinline__ uint32_t dynamic_smem_bytes()
     asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(r));
     return r;
 }
+#ifdef EXL3_PROFILE
+__device__ __forceinline__ long long global_ns()
+{
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#endif
 __device__ __forceinline__ void cluster_sync_all()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void cluster_arrive()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait()
+{
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void fence_cluster()
+{
+    asm volatile("fence.acq_rel.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v)
+{
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr)
 {
@@ -116,12 +141,6 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity)
     for (uint32_t i = 0; i < kWaitSpins; i++)
         if (mbar_try_wait_cluster(bar, parity)) return true;
     return false;
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr)
-{
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
-    return v;
 }
 
 // (w, w) from the two-halves word of 3INST / MCG, or from the MUL1 pattern.
@@ -167,12 +186,16 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
-    uint64_t* red_full = empty + kMaxStages;      // leader: partial sums of the other CTAs are ready
-    uint64_t* red_done = red_full + 1;            // non-leader: the leader has read my partial sums
+    uint64_t* red_full = empty + kMaxStages;      // leader: the other CTAs' partial sums have landed
+    uint64_t* red_done = red_full + 1;            // non-leader: the leader has emptied the landing slots
+    float* slots = reinterpret_cast<float*>(smem + a.slot_off);   // leader: (S-1) x rows x 128 floats
     float* ybuf = reinterpret_cast<float*>(smem + kHeaderBytes);
     uint8_t* xs = smem + kHeaderBytes + L::kYBytes;           // fused activations (XFUSED)
     uint8_t* stage0 = smem + a.stage0_off;
 
+#ifdef EXL3_PROFILE
+    const long long gt_entry = global_ns();
+#endif
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = a.ksplit;
     const int rank = S > 1 ? (int)cluster_ctarank() : 0;
@@ -256,13 +279,15 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
     // ----------------------------------------------------------------- consumers ----
 #ifdef EXL3_PROFILE
     long long pt_start = clock64(), pt_wait = 0, pt_comp = 0, pt_flush = 0;
+    const long long gt_init = global_ns();
+    long long gt_dep = 0;
 #endif
-    griddep_wait();   // x (and, for the leader, y) belong to earlier kernels until they end
-
     const int g = lane >> 2, tig = lane & 3;
     const int grp = warp >> 2, tnp = warp & 3;
     const int prev_word = (lane + 31) & 31;
-    const uint32_t sixteen = 16u;   // a literal: measured faster than keeping these shifts on the multiplier
+    // A literal 16: handing it in as a run-time value (so that the nibble shift becomes a wide
+    // multiply) was measured slower, twice — the multiplier pipe is as busy as the logic pipe.
+    const uint32_t sixteen = 16u;
     const uint32_t xor_const = a.cb_xor;   // 0x3B603B60, kept opaque on purpose (see exl3_bits.cuh)
     LaneWords<K> lw;
     lw.init(lane);
@@ -273,27 +298,30 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
     int xo[4] = {0, 0, 0, 0};  // TMA box: swizzled chunk offsets of the (tile-row parity, half) cases
     if (XFUSED) {
         const int rows = a.rows;
+        const int ntask = rows * klen;               // one (row, k-block) per warp and turn
         const int zero_off = klen * rows * kXsRowBytes;
-        // rotate this CTA's k-slice: one warp per (row, k-block)
-        for (int task = warp; task < rows * klen; task += kConsumerWarps) {
-            const int r = task / klen, kbl = task - r * klen;
-            const int64_t col = (int64_t)(kb0 + kbl) * 128 + lane * 4;
-            float v[4];
-            if (a.x_dtype == EXL3_DT_F16)
-                load4_any<__half>(reinterpret_cast<const __half*>(a.x) + (int64_t)r * a.x_row_stride + col, v);
+        auto task_col = [&](int task) {
+            const int r = task / klen;
+            return (int64_t)(kb0 + task - r * klen) * 128 + lane * 4;
+        };
+        auto load_scale = [&](int task, float (&sc)[4]) {
+            if (a.suh && task < ntask) load4_any<__half>(a.suh + task_col(task), sc);
+            else sc[0] = sc[1] = sc[2] = sc[3] = 1.f;
+        };
+        auto load_x = [&](int task, float (&v)[4]) {
+            if (task >= ntask) return;
+            const int r = task / klen;
+            const int64_t off = (int64_t)r * a.x_row_stride + task_col(task);
+            if (a.x_dtype == EXL3_DT_F16) load4_any<__half>(reinterpret_cast<const __half*>(a.x) + off, v);
             else if (a.x_dtype == EXL3_DT_BF16)
-                load4_any<__nv_bfloat16>(
-                    reinterpret_cast<const __nv_bfloat16*>(a.x) + (int64_t)r * a.x_row_stride + col, v);
-            else
-                load4_any<float>(reinterpret_cast<const float*>(a.x) + (int64_t)r * a.x_row_stride + col, v);
+                load4_any<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(a.x) + off, v);
+            else load4_any<float>(reinterpret_cast<const float*>(a.x) + off, v);
+        };
+        auto rotate_store = [&](int task, float (&v)[4], const float (&sc)[4]) {
+            if (task >= ntask) return;
+            const int r = task / klen, kbl = task - r * klen;
 #pragma unroll
-            for (int q = 0; q < 4; q++) v[q] = __half2float(__float2half_rn(v[q]));
-            if (a.suh) {
-                float sc[4];
-                load4_any<__half>(a.suh + col, sc);
-#pragma unroll
-                for (int q = 0; q < 4; q++) v[q] *= sc[q];
-            }
+            for (int q = 0; q < 4; q++) v[q] = __half2float(__float2half_rn(v[q])) * sc[q];
             had128_warp(v, lane);
             const uint32_t dupm = FAST ? 0x00010001u : 1u;
             uint4 e;
@@ -302,6 +330,25 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             e.z = (uint32_t)__half_as_ushort(__float2half_rn(v[2] * EXL3_HAD_SCALE)) * dupm;
             e.w = (uint32_t)__half_as_ushort(__float2half_rn(v[3] * EXL3_HAD_SCALE)) * dupm;
             *reinterpret_cast<uint4*>(xs + (kbl * rows + r) * kXsRowBytes + lane * 16) = e;
+        };
+        // suh is a weight: the first two turns' scales are fetched while the previous kernel
+        // of the stream may still be running; x belongs to it until the dependency wait.
+        float sc0[4], sc1[4], v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
+        load_scale(warp, sc0);
+        load_scale(warp + kConsumerWarps, sc1);
+        griddep_wait();
+#ifdef EXL3_PROFILE
+        gt_dep = global_ns();
+#endif
+        for (int task = warp; task < ntask; task += 2 * kConsumerWarps) {
+            if (task != warp) {
+                load_scale(task, sc0);
+                load_scale(task + kConsumerWarps, sc1);
+            }
+            load_x(task, v0);                       // both loads in flight before either is used
+            load_x(task + kConsumerWarps, v1);
+            rotate_store(task, v0, sc0);
+            rotate_store(task + kConsumerWarps, v1, sc1);
         }
         if (tid < kXsRowBytes / 4) reinterpret_cast<uint32_t*>(xs + zero_off)[tid] = 0u;
         // lanes whose batch row does not exist read the zero line
@@ -312,6 +359,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         const int v = (tig >> 1) ^ g;
 #pragma unroll
         for (int c = 0; c < 4; c++) xo[c] = (((2 * c) ^ v) << 4) + g * 128 + 8 * (tig & 1);
+        griddep_wait();   // y belongs to earlier kernels of the stream until they end
+#ifdef EXL3_PROFILE
+        gt_dep = global_ns();
+#endif
     }
 
     float acc[2][NMMA][4];
@@ -323,6 +374,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             for (int q = 0; q < 4; q++) acc[t][m][q] = 0.f;
 #ifdef EXL3_PROFILE
     long long pt_pro = clock64();
+    const long long gt_loop = global_ns();
 #endif
 
     bool failed = false;
@@ -330,7 +382,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
     int s = grp;                          // its ring stage (ns >= kGroups)
     uint32_t parity = 0;
     uint32_t red_parity = 0;              // phase of red_full (leader) / red_done (others)
-    bool red_pending = false;             // non-leader: the leader may still be reading ybuf
 
     for (int cbi = 0; cbi < n_cb; cbi++) {
         const int cb = cluster_id + cbi * n_clusters;
@@ -405,13 +456,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
 #endif
 
         // ---- block cb is done in this CTA: gather the partial sums ------------------------
-        if (red_pending) {   // the previous block's sums must have been read by the leader
-            if (!failed && !mbar_wait_cluster(smem_u32(red_done), red_parity ^ 1u)) {
-                failed = true;
-                if (lane == 0) atomicOr(a.status, ST_WAIT_FULL_TIMEOUT);
-            }
-            red_pending = false;
-        }
         float* yg = ybuf + grp * L::kYCopy;
 #pragma unroll
         for (int t = 0; t < 2; t++)
@@ -426,24 +470,39 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
                 for (int q = 0; q < 4; q++) acc[t][m][q] = 0.f;
             }
         named_bar_sync(1, kConsumerThreads);
-        // the groups' copies, added in a fixed order into copy 0
+        if (rank != 0) {
+            // The landing slots still hold the previous block until the leader says otherwise.
+            if (cbi > 0) {
+                if (!failed && !mbar_wait_cluster(smem_u32(red_done), red_parity)) {
+                    failed = true;
+                    if (lane == 0) atomicOr(a.status, ST_WAIT_FULL_TIMEOUT);
+                }
+                red_parity ^= 1u;
+            }
+            // the groups' copies, added in a fixed order, go straight into this CTA's slot
+            const uint32_t slot = map_to_cta(smem_u32(slots + (rank - 1) * a.rows * 128), 0);
+            if (!failed)
+                for (int i = tid; i < a.rows * 128; i += kConsumerThreads) {
+                    const int o = (i >> 7) * kYStride + (i & 127);
+                    float f = ybuf[o];
+#pragma unroll
+                    for (int c = 1; c < kGroups; c++) f += ybuf[o + c * L::kYCopy];
+                    st_cluster_f32(slot + 4u * (uint32_t)i, f);
+                }
+            fence_cluster();                       // my stores, before the arrive below, cluster-wide
+            named_bar_sync(1, kConsumerThreads);   // everybody's stores are issued; ybuf is free again
+            if (tid == 0 && !failed) mbar_arrive_remote(map_to_cta(smem_u32(red_full), 0));
+#ifdef EXL3_PROFILE
+            pt_flush += clock64() - f0;
+#endif
+            continue;
+        }
         for (int i = tid; i < a.rows * 128; i += kConsumerThreads) {
             const int o = (i >> 7) * kYStride + (i & 127);
             float f = ybuf[o];
 #pragma unroll
             for (int c = 1; c < kGroups; c++) f += ybuf[o + c * L::kYCopy];
             ybuf[o] = f;
-        }
-        named_bar_sync(1, kConsumerThreads);
-        if (rank != 0) {
-            // hand copy 0 to the leader; it tells us through red_done when it has read it
-            if (tid == 0) mbar_arrive_remote(map_to_cta(smem_u32(red_full), 0));
-            red_pending = true;
-            red_parity ^= 1u;
-#ifdef EXL3_PROFILE
-            pt_flush += clock64() - f0;
-#endif
-            continue;
         }
         if (S > 1) {
             if (!failed && !mbar_wait_cluster(smem_u32(red_full), red_parity)) {
@@ -452,6 +511,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             }
             red_parity ^= 1u;
         }
+        named_bar_sync(1, kConsumerThreads);
         const int sv_off = a.blocks ? a.blocks[cb].sv_off : cb * 128;
         const int y_off = a.blocks ? a.blocks[cb].y_off : cb * 128;
         for (int n = warp; n < a.rows; n += kConsumerWarps) {
@@ -461,9 +521,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             for (int q = 0; q < 4; q++) v[q] = ybuf[o + q];
             if (!failed)
                 for (int r = 1; r < S; r++) {   // the other CTAs' sums, in rank order
-                    const uint32_t ra = map_to_cta(smem_u32(ybuf + o), (uint32_t)r);
-#pragma unroll
-                    for (int q = 0; q < 4; q++) v[q] += ld_cluster_f32(ra + 4 * q);
+                    const float4 p = *reinterpret_cast<const float4*>(slots + ((r - 1) * a.rows + n) * 128 + 4 * lane);
+                    v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
                 }
 #pragma unroll
             for (int q = 0; q < 4; q++) v[q] = __half2float(__float2half_rn(v[q]));
@@ -489,28 +548,41 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             ov.y = h2_as_u32(h1);
             *reinterpret_cast<uint2*>(a.y + (int64_t)n * a.y_row_stride + y_off + 4 * lane) = ov;
         }
-        named_bar_sync(1, kConsumerThreads);   // all reads of ybuf (local and remote) are done
-        if (S > 1 && tid == 0)
-            for (int r = 1; r < S; r++) mbar_arrive_remote(map_to_cta(smem_u32(red_done), (uint32_t)r));
+        if (cbi + 1 < n_cb) {
+            // more blocks follow: tell the others that the landing slots are free again
+            named_bar_sync(1, kConsumerThreads);   // all reads of ybuf and of the slots are done
+            if (S > 1 && tid == 0)
+                for (int r = 1; r < S; r++) mbar_arrive_remote(map_to_cta(smem_u32(red_done), (uint32_t)r));
+        }
 #ifdef EXL3_PROFILE
         pt_flush += clock64() - f0;
 #endif
     }
 #ifdef EXL3_PROFILE
     long long pt_main = clock64();
+    const long long gt_main = global_ns();
 #endif
-    // A non-leader's shared memory must outlive the leader's last read of it.
-    if (red_pending && !failed) {
-        if (!mbar_wait_cluster(smem_u32(red_done), red_parity ^ 1u) && lane == 0)
-            atomicOr(a.status, ST_WAIT_FULL_TIMEOUT);
+    // The leader's shared memory is the target of the other CTAs' stores and arrives, so it
+    // leaves last: every CTA arrives at the cluster barrier, only the leader waits on it —
+    // also when a bounded wait above gave up.  (Threads that have exited count as arrived.)
+    if (S > 1) {
+        cluster_arrive();
+        if (rank == 0) cluster_wait();
     }
-    // No CTA of a cluster leaves while another may still arrive on its barriers or read its
-    // partial sums — also when a bounded wait above gave up.  (The producer lane has issued
-    // all its copies long before; threads that have exited do not take part.)
-    if (S > 1) cluster_sync_all();
 #ifdef EXL3_PROFILE
     if (a.prof && lane == 0) {
-        long long* p = a.prof + ((size_t)blockIdx.x * kConsumerWarps + warp) * 8;
+        long long* p = a.prof + ((size_t)blockIdx.x * kConsumerWarps + warp) * 16;
+        p[8] = gt_entry;               // wall clock (ns): kernel entry of this CTA
+        p[9] = gt_init;                // barriers set up, cluster synchronised
+        p[10] = gt_dep;                // previous kernel complete
+        p[11] = gt_loop;               // activations ready, main loop starts
+        p[12] = gt_main;               // main loop + gathers done
+        p[13] = global_ns();           // end
+        {
+            uint32_t smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            p[14] = smid;
+        }
         p[0] = pt_pro - pt_start;      // dependency wait + activation prologue
         p[1] = pt_wait;                // waiting for ring stages
         p[2] = pt_comp;                // decode + MMA
@@ -528,7 +600,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
 // tuning state and shape decisions live in exl3_gemv.cu
 extern int g_gemv_ctas_per_sm;
 extern int g_gemv_smem_budget;
-void gemv_choose_split(int ncb, int nkb, int* ksplit, int* grid);
+void gemv_choose_split(int ncb, int nkb, int rows, int* ksplit, int* grid);
 
 template <int K, int CB, int NMMA, bool FAST, bool XFUSED>
 static int launch_gemv_t(GemvArgs a, bool pdl, cudaStream_t s)
@@ -536,13 +608,15 @@ static int launch_gemv_t(GemvArgs a, bool pdl, cudaStream_t s)
     using L = GemvLayout<K, NMMA>;
     const int nkb = a.t_in >> 3;
     int ksplit, grid;
-    gemv_choose_split(a.ncb, nkb, &ksplit, &grid);
+    gemv_choose_split(a.ncb, nkb, a.rows, &ksplit, &grid);
     a.ksplit = ksplit;
     a.cb_xor = 0x3B603B60u;
     a.sixteen = 16u;
     const int klen_max = (nkb + ksplit - 1) / ksplit;
     const int xs_bytes = XFUSED ? (klen_max * a.rows + 1) * kXsRowBytes : 0;
-    const int stage0 = (kHeaderBytes + L::kYBytes + xs_bytes + 1023) / 1024 * 1024;
+    const int slot_bytes = (ksplit - 1) * a.rows * 512;
+    a.slot_off = kHeaderBytes + L::kYBytes + xs_bytes;
+    const int stage0 = (a.slot_off + slot_bytes + 1023) / 1024 * 1024;
     const int stage_bytes = (XFUSED ? 0 : L::kXBoxBytes) + L::kWeightBytes;
     int budget = g_gemv_smem_budget;
     int stages = (budget - stage0) / stage_bytes;

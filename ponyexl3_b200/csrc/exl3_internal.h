@@ -71,7 +71,8 @@ struct GemvArgs {
     uint32_t sixteen;          // the number 16 as a run-time value (keeps shifts on the multiplier)
     uint32_t cb_xor;           // XOR constant of the 3INST / MCG codebooks, as a run-time value
     int ksplit;                // CTAs per cluster = k-slices per column block
-    int stage0_off;            // byte offset of the ring inside dynamic shared memory            // 1: xh holds (x, x) and the MMA adds the codebook halves
+    int stage0_off;            // byte offset of the ring inside dynamic shared memory
+    int slot_off;              // byte offset of the leader's landing slots for the other CTAs' partial sums
 };
 
 int launch_gemv(const GemvArgs& a, int k, int cb, bool pdl, cudaStream_t s);
