@@ -86,8 +86,11 @@ class SyntheticDenseDecoder:
     over `rows` new positions and returns the arg-max token of every row."""
 
     def __init__(self, cfg: DenseConfig, device: torch.device, seed: int = 5000, group=None,
-                 pdl: bool = True, tensor_parallel: bool = True):
+                 pdl: bool = True, tensor_parallel: bool = True, native_glue: bool = True):
         self.cfg, self.dev, self.pg = cfg, device, group
+        # native_glue: norm / rotary + cache append / attention / SwiGLU through the library's
+        # step kernels (head_dim 128 only); otherwise the same math as PyTorch ops
+        self.native_glue = native_glue and cfg.head_dim == 128
         self.world = (dist.get_world_size(group)
                       if (tensor_parallel and dist.is_available() and dist.is_initialized()) else 1)
         self.rank = dist.get_rank(group) if self.world > 1 else 0
@@ -231,9 +234,31 @@ class SyntheticDenseDecoder:
         return out.view(self.hkv, c.group, rows, c.head_dim).permute(2, 0, 1, 3).reshape(rows, -1)
 
     # ---- the step ----------------------------------------------------------------------------
+    def _forward_native(self, tokens: torch.Tensor) -> torch.Tensor:
+        """The step with the library's glue kernels: 13 launches per layer on one GPU."""
+        from . import ops
+        c = self.cfg
+        rows = tokens.shape[0]
+        x = self.embed[tokens]                                            # (rows, hidden), updated in place
+        delta = None
+        for L in self.layers:
+            h = ops.add_rmsnorm(x, delta, L.norm1, c.rms_eps)
+            qkv = L.qkv.forward_packed(h)
+            q = ops.rope_append(qkv, self.cos, self.sin, L.k_cache, L.v_cache, self.hq, c.context)
+            a = ops.attn_decode(q, L.k_cache, L.v_cache, c.context)
+            a = self._gather(a, [(r * self.hq * 128, (r + 1) * self.hq * 128) for r in range(self.world)])
+            o = self._gather(L.o(a), self.hidden_spans)
+            h = ops.add_rmsnorm(x, o, L.norm2, c.rms_eps)
+            act = self._gather(ops.swiglu(L.gate_up.forward_packed(h)), self.inter_spans)
+            delta = self._gather(L.down(act), self.hidden_spans)
+        h = ops.add_rmsnorm(x, delta, self.final_norm, c.rms_eps)
+        return self.head(h)
+
     @torch.no_grad()
     def forward_logits(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens (rows,) int64 -> this rank's slice of the logits (rows, local vocab) fp16."""
+        if self.native_glue:
+            return self._forward_native(tokens)
         c = self.cfg
         rows = tokens.shape[0]
         hd = c.head_dim

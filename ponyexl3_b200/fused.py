@@ -116,6 +116,21 @@ class FusedEXL3Group(torch.nn.Module):
         return t
 
     @torch.no_grad()
+    def forward_packed(self, x2d: torch.Tensor) -> torch.Tensor:
+        """All members side by side, (rows, sum(out)) fp16, for 1..16 rows — one buffer a
+        following kernel can take whole (q|k|v for the rotary step, gate|up for SwiGLU)."""
+        rows = x2d.shape[0]
+        if not 1 <= rows <= GEMV_MAX_ROWS:
+            raise ValueError("forward_packed serves 1..16 rows")
+        blocks, row_src, suh_row = self._table(rows, x2d.device)
+        y = torch.empty((rows, int(self._offsets[-1])), dtype=torch.float16, device=x2d.device)
+        ops.gemv_blocks(x2d, xh_rows=rows * len(self._out_features), row_src=row_src,
+                        suh=self._suh_stack, suh_row=suh_row, trellis=self._trellis, k=self.k,
+                        cb=self.cb, blocks=blocks, rows=rows, svh=self._svh_cat, bias=None, y=y,
+                        pdl=self.pdl)
+        return y
+
+    @torch.no_grad()
     def forward_all(self, x: torch.Tensor) -> tuple[torch.Tensor, ...]:
         in_shape = x.shape
         if in_shape[-1] != self.in_features:

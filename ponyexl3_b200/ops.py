@@ -255,3 +255,77 @@ def gemm_tiles(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None,
         tiles.shape[0], ptr(svh), y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes, 0,
         _stream(x2d.device)), "exl3_gemm_tiles")
     return y
+
+
+# ---- the caller's side of a decode step (exl3_step.cu) ---------------------------------------
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """In place x <- x + delta (skipped when delta is None); returns fp16 RMSNorm(x) * weight.
+    x, delta (rows, n) fp16 with unit column stride."""
+    _need_cuda(x, "x")
+    rows, n = x.shape
+    h = out if out is not None else torch.empty((rows, n), dtype=torch.float16, device=x.device)
+    if delta is not None and delta.stride(1) != 1:
+        delta = delta.contiguous()
+    _lib.check(_lib.load().exl3_add_rmsnorm(
+        x.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(), h.data_ptr(), rows, n,
+        x.stride(0), 0 if delta is None else delta.stride(0), h.stride(0), float(eps), _stream(x.device)),
+        "exl3_add_rmsnorm")
+    return h
+
+
+def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_cache: torch.Tensor,
+                v_cache: torch.Tensor, q_heads: int, pos0: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """qkv (rows, (q_heads + 2 kv_heads) * 128) -> rotated q (rows, q_heads, 128); rotated k and
+    v are written to rows pos0.. of the caches (kv_heads, cache_len, 128)."""
+    _need_cuda(qkv, "qkv")
+    rows = qkv.shape[0]
+    kv_heads, cache_len, hd = k_cache.shape
+    if hd != 128 or qkv.shape[1] != (q_heads + 2 * kv_heads) * 128 or qkv.stride(1) != 1:
+        raise ValueError("rope_append expects head_dim 128 and a packed q|k|v row")
+    q = out if out is not None else torch.empty((rows, q_heads, 128), dtype=torch.float16, device=qkv.device)
+    _lib.check(_lib.load().exl3_rope_append(
+        qkv.data_ptr(), qkv.stride(0), cos.data_ptr(), sin.data_ptr(), q.data_ptr(), k_cache.data_ptr(),
+        v_cache.data_ptr(), rows, q_heads, kv_heads, cache_len, int(pos0), _stream(qkv.device)),
+        "exl3_rope_append")
+    return q
+
+
+_attn_ws: dict[int, torch.Tensor] = {}
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx: int,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """q (rows, q_heads, 128) over caches (kv_heads, cache_len, 128) that already hold the new
+    positions ctx .. ctx+rows-1 -> (rows, q_heads * 128); position r sees keys 0 .. ctx + r."""
+    _need_cuda(q, "q")
+    rows, q_heads, hd = q.shape
+    kv_heads, cache_len, _ = k_cache.shape
+    lib = _lib.load()
+    need = int(lib.exl3_attn_workspace_bytes(rows, q_heads, kv_heads, ctx + rows))
+    if need == 0 or hd != 128:
+        raise ValueError("unsupported attention shape")
+    idx = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    ws = _attn_ws.get(idx)
+    if ws is None or ws.numel() < need:
+        if ws is not None:
+            torch.cuda.current_stream(q.device).synchronize()
+        ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+        _attn_ws[idx] = ws
+    y = out if out is not None else torch.empty((rows, q_heads * 128), dtype=torch.float16, device=q.device)
+    _lib.check(lib.exl3_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), y.data_ptr(), rows,
+                                    q_heads, kv_heads, cache_len, int(ctx), ws.data_ptr(), ws.numel(),
+                                    _stream(q.device)), "exl3_attn_decode")
+    return y
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """gate_up (rows, 2h) = [gate | up] -> fp16 silu(gate) * up, (rows, h)."""
+    _need_cuda(gate_up, "gate_up")
+    rows, two_h = gate_up.shape
+    h = two_h // 2
+    y = out if out is not None else torch.empty((rows, h), dtype=torch.float16, device=gate_up.device)
+    _lib.check(_lib.load().exl3_swiglu(gate_up.data_ptr(), gate_up.stride(0), y.data_ptr(), y.stride(0), rows, h,
+                                       _stream(gate_up.device)), "exl3_swiglu")
+    return y
