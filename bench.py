@@ -179,6 +179,30 @@ def run_reference(args):
 
 # ------------------------------------------------------------------------ GPU arm -----
 
+def finish_ranks(dist):
+    """End of a multi-rank run (the caller has dropped its CUDA graph: captured NCCL kernels
+    must be gone before the communicator).  If tearing the process group down still does not
+    return promptly, the ranks leave without it — their results are already printed."""
+    import gc
+    import torch
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    done = threading.Event()
+
+    def teardown():
+        try:
+            dist.destroy_process_group()
+        finally:
+            done.set()
+
+    threading.Thread(target=teardown, daemon=True).start()
+    if not done.wait(20.0):
+        os._exit(0)
+
+
 def shard_cols(outf: int, world: int, rank: int):
     """Column range owned by `rank` (tensor parallel by output tile, whole 128-column blocks)."""
     from ponyexl3_b200.parallel import shard_columns
@@ -403,7 +427,8 @@ def run_gpu(args):
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.destroy_process_group()
+        graph = None          # the captured NCCL kernels go before the communicator does
+        finish_ranks(dist)
 
 
 def run_decode(args):
@@ -546,7 +571,8 @@ def run_decode(args):
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.destroy_process_group()
+        graph = None          # the captured NCCL kernels go before the communicator does
+        finish_ranks(dist)
 
 
 def run_sweep(args):
