@@ -227,6 +227,34 @@ EXL3_API int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, const 
 EXL3_API int exl3_swiglu(const uint16_t* gate_up, int64_t gu_row_stride, uint16_t* out, int64_t out_row_stride,
                          int rows, int64_t h, exl3_stream_t stream);
 
+/* ---- output exchange over peer memory (tensor parallel by output tile) -------------------
+ * The reference is single-device; sharding a linear by output tile (ponyexl3/ref/reconstruct.py:13-23
+ * decodes any 128-aligned column range on its own) needs the slices of a row gathered on every GPU
+ * before the next layer.  These entry points do that with plain loads and stores over NVLink: the
+ * caller maps every rank's full-row buffer and arrival counter into every process (one process per
+ * GPU) and passes the W device pointers as HOST arrays.
+ *
+ * exl3_gemv_peers: exl3_gemv whose epilogue stores each finished 128-column block at column
+ *   col0 + block * 128 of EVERY rank's (rows, full_row_stride) buffer and then adds 1 to every
+ *   rank's counter.  A rank's full row is complete when its counter has grown by the number of
+ *   blocks of the whole layer (out_features_total / 128).
+ * exl3_peer_allgather: the same exchange for a (rows, cols) slice computed by other kernels;
+ *   one arrival per rank, so the full row is complete after n_peers arrivals.
+ * exl3_peer_wait: one-thread kernel that polls this rank's counter until `target` arrivals are
+ *   there, subtracts them again and ends.  The poll gives up after about a second and sets bit 16
+ *   in the status word of `workspace` (exl3_workspace_status).  A (buffer, counter) pair must not be
+ *   the target of two consecutive exchanges: rotate over at least two pairs. */
+EXL3_API int exl3_gemv_peers(const void* x, int x_dtype, int rows, int64_t x_row_stride,
+                             const uint16_t* trellis, int64_t t_in, int64_t t_out, int k, int cb,
+                             const uint16_t* suh, const uint16_t* svh, const uint16_t* bias,
+                             const uint64_t* y_peers, const uint64_t* counter_peers, int n_peers,
+                             int64_t full_row_stride, int64_t col0, void* workspace, size_t workspace_bytes,
+                             unsigned flags, exl3_stream_t stream);
+EXL3_API int exl3_peer_allgather(const uint16_t* src, int rows, int64_t cols, int64_t src_row_stride,
+                                 const uint64_t* dst_peers, const uint64_t* counter_peers, int n_peers,
+                                 int64_t dst_row_stride, int64_t col0, exl3_stream_t stream);
+EXL3_API int exl3_peer_wait(uint32_t* counter, uint32_t target, void* workspace, exl3_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,6 +60,12 @@ _PROTOTYPES = {
     "exl3_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int,
                                  c_void_p, c_size_t, c_void_p]),
     "exl3_swiglu": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_void_p]),
+    "exl3_gemv_peers": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
+                                c_void_p, c_size_t, c_uint, c_void_p]),
+    "exl3_peer_allgather": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64,
+                                    c_int64, c_void_p]),
+    "exl3_peer_wait": (c_int, [c_void_p, c_uint, c_void_p, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

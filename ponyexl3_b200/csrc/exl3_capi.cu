@@ -201,10 +201,18 @@ int exl3_workspace_status(const void* workspace, int* status_out, exl3_stream_t 
     return note_cuda(cudaStreamSynchronize((cudaStream_t)stream));
 }
 
-int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const uint16_t* trellis,
-              int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
-              const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
-              size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+// Peer description of the fused output all-gather (n == 0: plain local output).
+struct PeerOut {
+    int n = 0;
+    int64_t col0 = 0;
+    const uint64_t* y = nullptr;      // host arrays of device pointers
+    const uint64_t* ctr = nullptr;
+};
+
+static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_stride, const uint16_t* trellis,
+                       int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
+                       const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
+                       size_t workspace_bytes, unsigned flags, exl3_stream_t stream, const PeerOut& peer)
 {
     if (!x || !trellis || !y) return EXL3_E_NULL;
     if (k < 1 || k > 8) return EXL3_E_K;
@@ -265,7 +273,46 @@ int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const 
         a.prof = reinterpret_cast<long long*>(ws + kWsScratch) + (size_t)(prof_launch++ & 1) * 400 * 16 * 16;
     }
 #endif
+    a.n_peer = peer.n;
+    a.y_col0 = peer.col0;
+    for (int p = 0; p < peer.n; p++) {
+        a.y_peer[p] = reinterpret_cast<__half*>(peer.y[p]);
+        a.ctr_peer[p] = reinterpret_cast<unsigned*>(peer.ctr[p]);
+    }
     return launch_gemv(a, k, cb, pdl, s);
+}
+
+int exl3_gemv(const void* x, int x_dtype, int rows, int64_t x_row_stride, const uint16_t* trellis,
+              int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
+              const uint16_t* bias, uint16_t* y, int64_t y_row_stride, void* workspace,
+              size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+{
+    return gemv_common(x, x_dtype, rows, x_row_stride, trellis, t_in, t_out, k, cb, suh, svh, bias, y,
+                       y_row_stride, workspace, workspace_bytes, flags, stream, PeerOut{});
+}
+
+int exl3_gemv_peers(const void* x, int x_dtype, int rows, int64_t x_row_stride, const uint16_t* trellis,
+                    int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
+                    const uint16_t* bias, const uint64_t* y_peers, const uint64_t* counter_peers, int n_peers,
+                    int64_t full_row_stride, int64_t col0, void* workspace, size_t workspace_bytes,
+                    unsigned flags, exl3_stream_t stream)
+{
+    if (!y_peers || !counter_peers) return EXL3_E_NULL;
+    if (n_peers < 1 || n_peers > kMaxPeers) return EXL3_E_RANGE;
+    if (col0 < 0 || col0 % 128 || col0 + 16 * t_out > full_row_stride) return EXL3_E_SHAPE;
+    for (int p = 0; p < n_peers; p++) {
+        if (!y_peers[p] || !counter_peers[p]) return EXL3_E_NULL;
+        if (y_peers[p] % 8 || counter_peers[p] % 4) return EXL3_E_ALIGN;
+    }
+    PeerOut peer;
+    peer.n = n_peers;
+    peer.col0 = col0;
+    peer.y = y_peers;
+    peer.ctr = counter_peers;
+    // the local y of the plain entry point is unused; hand in rank 0's buffer for the checks
+    return gemv_common(x, x_dtype, rows, x_row_stride, trellis, t_in, t_out, k, cb, suh, svh, bias,
+                       reinterpret_cast<uint16_t*>(y_peers[0]), full_row_stride, workspace, workspace_bytes,
+                       flags, stream, peer);
 }
 
 int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,

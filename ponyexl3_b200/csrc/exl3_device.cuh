@@ -17,6 +17,7 @@ enum : int {
     ST_WAIT_EMPTY_TIMEOUT = 2,   // the producer gave up waiting for a free stage
     ST_TC_TIMEOUT = 4,           // a tensor-core pipeline wait gave up
     ST_BAD_LAUNCH = 8,           // a kernel found its launch (shared memory, cluster) not as planned
+    ST_PEER_TIMEOUT = 16,        // a wait for the other GPUs' output blocks gave up
 };
 
 // ---- codebooks: exact fp16 arithmetic -------------------------------------------------

@@ -546,7 +546,19 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
             uint2 ov;
             ov.x = h2_as_u32(h0);
             ov.y = h2_as_u32(h1);
-            *reinterpret_cast<uint2*>(a.y + (int64_t)n * a.y_row_stride + y_off + 4 * lane) = ov;
+            if (a.n_peer == 0) {
+                *reinterpret_cast<uint2*>(a.y + (int64_t)n * a.y_row_stride + y_off + 4 * lane) = ov;
+            } else {
+                // all-gather fused into the epilogue: the block lands in every rank's full row
+                const int64_t off = (int64_t)n * a.y_row_stride + a.y_col0 + y_off + 4 * lane;
+                for (int p = 0; p < a.n_peer; p++) *reinterpret_cast<uint2*>(a.y_peer[p] + off) = ov;
+                __threadfence_system();
+            }
+        }
+        if (a.n_peer > 0) {
+            named_bar_sync(1, kConsumerThreads);          // every row of the block has been sent
+            if (tid < a.n_peer)
+                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.ctr_peer[tid]) : "memory");
         }
         if (cbi + 1 < n_cb) {
             // more blocks follow: tell the others that the landing slots are free again

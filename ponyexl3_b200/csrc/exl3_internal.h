@@ -73,7 +73,14 @@ struct GemvArgs {
     int ksplit;                // CTAs per cluster = k-slices per column block
     int stage0_off;            // byte offset of the ring inside dynamic shared memory
     int slot_off;              // byte offset of the leader's landing slots for the other CTAs' partial sums
+    // output all-gather over peer memory (tensor parallel by output tile): when n_peer > 0 every
+    // finished block is stored into each rank's full-width row buffer and announced on its counter
+    int n_peer;
+    int64_t y_col0;            // this rank's first column inside the full row
+    __half* y_peer[8];         // full-width (rows, y_row_stride) buffers of all ranks, this one included
+    unsigned* ctr_peer[8];     // arrival counters of all ranks (one increment per finished block)
 };
+constexpr int kMaxPeers = 8;
 
 int launch_gemv(const GemvArgs& a, int k, int cb, bool pdl, cudaStream_t s);
 bool gemv_x_is_fused(int rows, int t_in, int ncb);

@@ -86,7 +86,8 @@ class SyntheticDenseDecoder:
     over `rows` new positions and returns the arg-max token of every row."""
 
     def __init__(self, cfg: DenseConfig, device: torch.device, seed: int = 5000, group=None,
-                 pdl: bool = True, tensor_parallel: bool = True, native_glue: bool = True):
+                 pdl: bool = True, tensor_parallel: bool = True, native_glue: bool = True,
+                 peer_exchange: bool = True):
         self.cfg, self.dev, self.pg = cfg, device, group
         # native_glue: norm / rotary + cache append / attention / SwiGLU through the library's
         # step kernels (head_dim 128 only); otherwise the same math as PyTorch ops
@@ -95,6 +96,14 @@ class SyntheticDenseDecoder:
                       if (tensor_parallel and dist.is_available() and dist.is_initialized()) else 1)
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         W, R = self.world, self.rank
+        # peer_exchange: the four all-gathers of a layer go over peer memory (the o / down GEMVs
+        # store their blocks into every rank's row, attention and SwiGLU outputs are copied the same
+        # way); otherwise NCCL all-gathers
+        self.peer = None
+        if W > 1 and peer_exchange and self.native_glue:
+            from .parallel import PeerExchange
+            self.peer = PeerExchange(cfg.max_rows, max(cfg.intermediate, cfg.q_heads * cfg.head_dim),
+                                     group, ring=PeerExchange.ring_for(4 * cfg.layers))
         if cfg.kv_heads % W:
             raise ValueError(f"{cfg.kv_heads} KV heads do not split over {W} ranks")
         self.ks = draw_bit_widths(cfg, seed)
@@ -150,7 +159,7 @@ class SyntheticDenseDecoder:
                                                     suh=_rand_signs(cfg.intermediate, device, gen), svh=sv,
                                                     key=f"l{li}.down")
             for m in (L.qkv, L.o, L.gate_up, L.down):
-                m.pdl = pdl and W == 1        # between NCCL kernels plain stream order is kept
+                m.pdl = pdl and (W == 1 or self.peer is not None)   # between NCCL kernels: plain stream order
                 self.packed_local += m.packed_bytes
             L.norm1 = torch.ones(d, dtype=torch.float16, device=device)
             L.norm2 = torch.ones(d, dtype=torch.float16, device=device)
@@ -165,7 +174,7 @@ class SyntheticDenseDecoder:
         tr, sv = columns(d, cfg.vocab, k_head, [self.vocab_span])
         self.head = EXL3Linear.from_device_tensors(trellis=tr, k=k_head, cb=cb, suh=_rand_signs(d, device, gen),
                                                    svh=sv, key="lm_head")
-        self.head.pdl = pdl and W == 1
+        self.head.pdl = pdl and (W == 1 or self.peer is not None)
         self.packed_local += self.head.packed_bytes
         self.final_norm = torch.ones(d, dtype=torch.float16, device=device)
         self.embed = torch.randn((cfg.vocab, d), device=device, generator=gen).to(torch.float16)
@@ -239,18 +248,34 @@ class SyntheticDenseDecoder:
         from . import ops
         c = self.cfg
         rows = tokens.shape[0]
+        q_all = c.q_heads * 128
+        peer = self.peer
+        if peer is not None:
+            peer.restart()
+
+        def gather(t, spans, total):
+            if peer is None:
+                return self._gather(t, spans)
+            return ops.peer_allgather(t, exchange=peer, cols_total=total, col0=spans[self.rank][0])
+
+        def linear_gather(m, t, spans, total):
+            if peer is None:
+                return self._gather(m(t), spans)
+            return ops.gemv_peers(t, m._trellis, m.k, m.cb, m._suh, m._svh, m._bias, exchange=peer,
+                                  out_features_total=total, col0=spans[self.rank][0], pdl=m.pdl)
+
+        head_spans = [(r * self.hq * 128, (r + 1) * self.hq * 128) for r in range(self.world)]
         x = self.embed[tokens]                                            # (rows, hidden), updated in place
         delta = None
         for L in self.layers:
             h = ops.add_rmsnorm(x, delta, L.norm1, c.rms_eps)
             qkv = L.qkv.forward_packed(h)
             q = ops.rope_append(qkv, self.cos, self.sin, L.k_cache, L.v_cache, self.hq, c.context)
-            a = ops.attn_decode(q, L.k_cache, L.v_cache, c.context)
-            a = self._gather(a, [(r * self.hq * 128, (r + 1) * self.hq * 128) for r in range(self.world)])
-            o = self._gather(L.o(a), self.hidden_spans)
+            a = gather(ops.attn_decode(q, L.k_cache, L.v_cache, c.context), head_spans, q_all)
+            o = linear_gather(L.o, a, self.hidden_spans, c.hidden)
             h = ops.add_rmsnorm(x, o, L.norm2, c.rms_eps)
-            act = self._gather(ops.swiglu(L.gate_up.forward_packed(h)), self.inter_spans)
-            delta = self._gather(L.down(act), self.hidden_spans)
+            act = gather(ops.swiglu(L.gate_up.forward_packed(h)), self.inter_spans, c.intermediate)
+            delta = linear_gather(L.down, act, self.hidden_spans, c.hidden)
         h = ops.add_rmsnorm(x, delta, self.final_norm, c.rms_eps)
         return self.head(h)
 

@@ -329,3 +329,47 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tens
     _lib.check(_lib.load().exl3_swiglu(gate_up.data_ptr(), gate_up.stride(0), y.data_ptr(), y.stride(0), rows, h,
                                        _stream(gate_up.device)), "exl3_swiglu")
     return y
+
+
+# ---- output exchange over peer memory (exl3_peer.cu) -----------------------------------------
+
+def gemv_peers(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh, svh, bias, *, exchange,
+               out_features_total: int, col0: int, pdl: bool = False) -> torch.Tensor:
+    """exl3_gemv whose output blocks land in every rank's full row (`exchange`: a
+    parallel.PeerExchange), followed by the wait for everybody's blocks.  Returns this rank's
+    complete (rows, out_features_total) row buffer."""
+    _need_cuda(x2d, "x")
+    rows, in_features = x2d.shape
+    t_in, t_out, _ = trellis.shape
+    if in_features != t_in * 16:
+        raise ValueError(f"x has {in_features} features, layer expects {t_in * 16}")
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    lib = _lib.load()
+    ws = Workspace.get(x2d.device, rows, in_features)
+    _, y_ptrs, c_ptrs, view, my_ctr = exchange.take(rows, out_features_total)
+    ptr = lambda t: None if t is None else t.data_ptr()
+    _lib.check(lib.exl3_gemv_peers(
+        x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out, k, int(cb),
+        ptr(suh), ptr(svh), ptr(bias), y_ptrs, c_ptrs, exchange.world, out_features_total, int(col0),
+        ws.buf.data_ptr(), ws.nbytes, _lib.FLAG_PDL if pdl else 0, _stream(x2d.device)), "exl3_gemv_peers")
+    _lib.check(lib.exl3_peer_wait(my_ctr, out_features_total // 128, ws.buf.data_ptr(), _stream(x2d.device)),
+               "exl3_peer_wait")
+    return view
+
+
+def peer_allgather(y_local: torch.Tensor, *, exchange, cols_total: int, col0: int) -> torch.Tensor:
+    """(rows, local) slice -> this rank's complete (rows, cols_total) row, over peer memory."""
+    _need_cuda(y_local, "y_local")
+    rows, cols = y_local.shape
+    if y_local.stride(1) != 1:
+        y_local = y_local.contiguous()
+    lib = _lib.load()
+    ws = Workspace.get(y_local.device, 1, 128)
+    _, y_ptrs, c_ptrs, view, my_ctr = exchange.take(rows, cols_total)
+    _lib.check(lib.exl3_peer_allgather(y_local.data_ptr(), rows, cols, y_local.stride(0), y_ptrs, c_ptrs,
+                                       exchange.world, cols_total, int(col0), _stream(y_local.device)),
+               "exl3_peer_allgather")
+    _lib.check(lib.exl3_peer_wait(my_ctr, exchange.world, ws.buf.data_ptr(), _stream(y_local.device)),
+               "exl3_peer_wait")
+    return view

@@ -181,3 +181,67 @@ def return_rows_to_tokens(y_rows: torch.Tensor, book, group=None) -> torch.Tenso
     out = torch.empty_like(back)
     out[order] = back
     return out.reshape(T, kk, -1)
+
+
+# ---- output exchange over peer memory ----------------------------------------------------------
+
+class PeerExchange:
+    """Full-row buffers and arrival counters of all ranks, mapped into every process
+    (torch symmetric memory: CUDA virtual-memory handles exchanged over the process group), for
+    the library's peer-store all-gather (`exl3_gemv_peers`, `exl3_peer_allgather`,
+    `exl3_peer_wait`).
+
+    `ring` (buffer, counter) pairs are used in rotation; two CONSECUTIVE exchanges must not share
+    a pair (a fast rank may send exchange j+1 while a slow one still reads j), so a caller that
+    replays a fixed sequence of G exchanges (a captured step) needs (G - 1) % ring != 0 — see
+    `ring_for`."""
+
+    def __init__(self, max_rows: int, max_cols: int, group=None, ring: int = 4):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 peers")
+        self.ring, self.max_rows, self.max_cols = ring, max_rows, max_cols
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.slot_elems = max_rows * max_cols
+        # one allocation: the row buffers of the ring, then the counters (256 B apart)
+        self._ctr_off = (ring * self.slot_elems * 2 + 255) // 256 * 256
+        nbytes = self._ctr_off + ring * 256
+        self.buf = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        torch.cuda.synchronize()
+        self.handle = symm.rendezvous(self.buf, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        dist.barrier(self.group)                      # everybody's counters are zero before first use
+        self._u64 = ctypes.c_uint64 * self.world
+        self._next = 0
+
+    @staticmethod
+    def ring_for(exchanges_per_replay: int) -> int:
+        """Smallest ring >= 3 whose rotation never puts the last exchange of a replayed sequence and
+        the first of the next replay on the same pair."""
+        r = 3
+        while (exchanges_per_replay - 1) % r == 0 and exchanges_per_replay > 1:
+            r += 1
+        return r
+
+    def restart(self) -> None:
+        """Start the rotation over (call at the top of every step, eager or captured)."""
+        self._next = 0
+
+    def take(self, rows: int, cols: int):
+        """Next pair of the ring: (slot index, host arrays of all ranks' buffer and counter pointers,
+        this rank's (rows, cols) view of its buffer, this rank's counter address)."""
+        if rows > self.max_rows or rows * cols > self.slot_elems:
+            raise ValueError("exchange larger than the ring's slots")
+        s = self._next
+        self._next = (s + 1) % self.ring
+        y = self._u64(*[p + s * self.slot_elems * 2 for p in self.ptrs])
+        c = self._u64(*[p + self._ctr_off + s * 256 for p in self.ptrs])
+        base = s * self.slot_elems * 2
+        view = self.buf[base:base + rows * cols * 2].view(torch.float16).view(rows, cols)
+        return s, y, c, view, self.ptrs[self.rank] + self._ctr_off + s * 256

@@ -99,16 +99,25 @@ def _dense_step(rank, world):
     cfg = DenseConfig(layers=2, hidden=512, intermediate=768, q_heads=4, kv_heads=2, head_dim=128,
                       vocab=1152, context=40, max_rows=4)
     one = SyntheticDenseDecoder(cfg, dev, seed=21, tensor_parallel=False)
-    tp = SyntheticDenseDecoder(cfg, dev, seed=21)
-    assert tp.world == world and one.world == 1
+    tp = SyntheticDenseDecoder(cfg, dev, seed=21)                        # exchanges over peer memory
+    tp_nccl = SyntheticDenseDecoder(cfg, dev, seed=21, peer_exchange=False)
+    assert tp.world == world and one.world == 1 and tp.peer is not None and tp_nccl.peer is None
     for rows in (1, 3):
         tok = torch.tensor([3, 700, 41][:rows], device=dev)
         want = one.forward_logits(tok).float()
         v0, v1 = tp.vocab_span
-        got = tp.forward_logits(tok).float()
-        err = (got - want[:, v0:v1]).norm() / want[:, v0:v1].norm()
-        assert float(err) < 2e-3, f"rank {rank} rows {rows}: {float(err)}"
-        assert torch.equal(tp.step(tok), one.step(tok))
+        for name, m in (("peer", tp), ("nccl", tp_nccl)):
+            got = m.forward_logits(tok).float()
+            err = (got - want[:, v0:v1]).norm() / want[:, v0:v1].norm()
+            assert float(err) < 2e-3, f"rank {rank} rows {rows} {name}: {float(err)}"
+            assert torch.equal(m.step(tok), one.step(tok))
+    # many steps back to back: the ring of buffers and counters keeps the ranks apart
+    tok = torch.tensor([5], device=dev)
+    ref = tp_nccl.step(tok)
+    for _ in range(20):
+        assert torch.equal(tp.step(tok), ref)
+    from ponyexl3_b200 import ops
+    assert ops.Workspace.get(dev, 1, 128).status() == 0
 
 
 def test_tensor_parallel_two_gpus_equals_one():
