@@ -257,10 +257,23 @@ def run_gpu(args):
           for inf in {s[0] for s in SHAPES}}
     from ponyexl3_b200.parallel import all_gather_columns
 
+    # N > 1: every layer's output row is completed on every rank.  Default: the GEMV epilogue
+    # stores its blocks into all ranks' rows over peer memory (exl3_gemv_peers) and a one-thread
+    # kernel waits for the arrivals; --nccl-gather uses an NCCL all-gather per layer instead.
+    peer = None
+    if dist is not None and not args.nccl_gather:
+        from ponyexl3_b200.parallel import PeerExchange
+        peer = PeerExchange(ROWS, max(s[1] for s in SHAPES), ring=PeerExchange.ring_for(len(layers)))
+
     def one_layer(L, x):
-        # programmatic launch only on one GPU: between NCCL kernels plain stream order is kept
-        ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=(dist is None), out=L.y)
-        if dist is not None:
+        if dist is None:
+            ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=True, out=L.y)
+        elif peer is not None:
+            L.y_full = ops.gemv_peers(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, exchange=peer,
+                                      out_features_total=L.outf, col0=L.c0, pdl=True)
+        else:
+            # between NCCL kernels plain stream order is kept (no programmatic launch)
+            ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=False, out=L.y)
             if ROWS == 1 and (L.outf // 128) % world == 0:
                 # one row, even split: the gathered chunks ARE the full row, no reshuffle
                 dist.all_gather_into_tensor(L.y_full.view(-1), L.y.view(-1))
@@ -268,6 +281,8 @@ def run_gpu(args):
                 L.y_full = all_gather_columns(L.y, L.outf)
 
     def step_body():
+        if peer is not None:
+            peer.restart()
         for L in layers:
             one_layer(L, xs[L.inf])
 
@@ -340,18 +355,23 @@ def run_gpu(args):
         mods.append(m)
     h_in = {inf: torch.randn((ROWS, inf)).to(torch.float16).pin_memory() for inf in xs}
     d_in = {inf: torch.empty_like(xs[inf]) for inf in xs}
-    h_out = [torch.empty((ROWS, m.out_features), dtype=torch.float16).pin_memory() for m in mods]
+    h_out = [torch.empty((ROWS, m.out_features if dist is None else m.full_out), dtype=torch.float16).pin_memory()
+             for m in mods]
     h2d = sum(v.numel() * 2 for v in h_in.values())
     d2h = sum(v.numel() * 2 for v in h_out)
 
     def e2e_step():
         for inf in h_in:
             d_in[inf].copy_(h_in[inf], non_blocking=True)
-        for m, ho in zip(mods, h_out):
-            y_loc = m(d_in[m.in_features])
-            if dist is not None:
-                all_gather_columns(y_loc, m.full_out)
-            ho.copy_(y_loc, non_blocking=True)
+        if dist is None:
+            for m, ho in zip(mods, h_out):
+                ho.copy_(m(d_in[m.in_features]), non_blocking=True)
+        else:
+            if peer is not None:
+                peer.restart()
+            for L, ho in zip(layers, h_out):
+                one_layer(L, d_in[L.inf])
+                ho.copy_(L.y_full, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = max(3, min(args.steps, 20))
@@ -402,7 +422,9 @@ def run_gpu(args):
                 "l2": f"inputs larger than L2: {step_bytes_global / world / 1e6:.0f} MB of distinct "
                       f"weights per GPU per step vs 126 MB L2",
                 "launch": "cuda_graph" if graph is not None else "eager",
-                "parallelism": f"tp{world} by output tile + all-gather" if world > 1 else "single GPU",
+                "parallelism": (f"tp{world} by output tile, output rows completed over peer memory in the "
+                                f"GEMV epilogue" if peer is not None else
+                                f"tp{world} by output tile + NCCL all-gather") if world > 1 else "single GPU",
             },
             "roofline": {
                 "bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
@@ -455,7 +477,7 @@ def run_decode(args):
     from ponyexl3_b200.dense_step import DenseConfig, SyntheticDenseDecoder
 
     cfg = DenseConfig(layers=args.layers, max_rows=max(16, args.rows))
-    dec = SyntheticDenseDecoder(cfg, dev, seed=5000)
+    dec = SyntheticDenseDecoder(cfg, dev, seed=5000, peer_exchange=not args.nccl_gather)
     rows = args.rows
     tok_in = torch.randint(0, cfg.vocab, (rows,), device=dev, generator=torch.Generator(device=dev).manual_seed(5))
     stream = torch.cuda.Stream(device=dev)
@@ -555,9 +577,11 @@ def run_decode(args):
                 "packed_bytes_per_gpu": dec.packed_local, "kv_bytes_per_gpu": dec.kv_bytes_local,
                 "l2": "weights + KV per GPU per step far larger than the 126 MB L2",
                 "launch": "cuda_graph" if graph is not None else "eager",
-                "parallelism": f"tp{world} by output tile, heads sharded, 4 all-gathers per layer"
+                "parallelism": (f"tp{world} by output tile, heads sharded, 4 exchanges per layer over "
+                                + ("peer memory" if dec.peer is not None else "NCCL all-gather"))
                                if world > 1 else "single GPU",
-                "glue": "RMSNorm, RoPE, attention (SDPA), SwiGLU, residual adds are PyTorch ops",
+                "glue": "residual+RMSNorm, rotary+cache append, split-context GQA attention, SwiGLU: library "
+                        "kernels; embedding gather and arg-max: PyTorch",
             },
             "roofline": {"bound": "hbm", "achieved": bytes_gpu / step_s / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": bytes_gpu / step_s / 1e9 / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
@@ -566,7 +590,9 @@ def run_decode(args):
             "e2e": {"value": rows / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8 * rows,
                     "d2h_bytes_per_step": 8 * rows, "ms_per_step": 1e3 * e2e_s,
                     "api": "SyntheticDenseDecoder.step, token ids from and to pinned host memory"},
-            "gpu_launches": (cfg.layers * 6 + 1) * args.steps,
+            # per layer: 2 norms, 2 rotations, 4 GEMVs, rotary, 2 attention, SwiGLU (+ 2 copies and 4
+            # waits with the peer exchange); then the final norm and the head
+            "gpu_launches": (cfg.layers * (12 + (6 if dec.peer is not None else 0)) + 2) * args.steps,
             "clocks": clocks, "kernel_status": status,
         }
         print(json.dumps(line), flush=True)
@@ -688,6 +714,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ring", type=int, default=16, help="layer sets per step")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="N > 1: NCCL all-gather per layer instead of the peer-memory epilogue")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--profile-case", choices=["gemv", "gemm"], default=None,
                     help="run one small case for an ncu capture and exit")
