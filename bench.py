@@ -174,10 +174,33 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------ GPU arm -----
+
+_RESULT_FD = None
+
+
+def quiet_stdout():
+    """Libraries print banners on stdout (NCCL's version line, for one); the result line must be
+    the only thing there.  Everything written to fd 1 from here on goes to stderr; `emit` writes
+    the result to the real stdout."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
 
 def finish_ranks(dist):
     """End of a multi-rank run (the caller has dropped its CUDA graph: captured NCCL kernels
@@ -447,7 +470,7 @@ def run_gpu(args):
             "clocks": clocks,
             "kernel_status": status,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         graph = None          # the captured NCCL kernels go before the communicator does
         finish_ranks(dist)
@@ -595,7 +618,7 @@ def run_decode(args):
             "gpu_launches": (cfg.layers * (12 + (6 if dec.peer is not None else 0)) + 2) * args.steps,
             "clocks": clocks, "kernel_status": status,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         graph = None          # the captured NCCL kernels go before the communicator does
         finish_ranks(dist)
@@ -731,6 +754,8 @@ def main():
     ap.add_argument("--rows", type=int, default=1, help="decode workload: new positions per step (1 or 16)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: transformer layers")
     args = ap.parse_args()
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        quiet_stdout()
     if args.sweep:
         run_sweep(args)
         return

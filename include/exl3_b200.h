@@ -199,13 +199,15 @@ EXL3_API int exl3_gemv_noalloc(const void* x, int x_dtype, int rows, int64_t x_r
  * mlx.fast.rope, mlx.fast.scaled_dot_product_attention; linears installed at
  * ponyexl3/mlx/model.py:628-634), so they replace no reference code of the path; they exist so
  * that a whole decode step can run as a short train of launches.  fp16 tensors, fp32 math,
- * head_dim 128, device pointers, nothing allocated. */
+ * head_dim 128, device pointers, nothing allocated.  flags: EXL3_FLAG_PDL launches the kernel
+ * with programmatic stream serialization (it may start while its predecessor drains; it waits
+ * for the predecessor's results before touching memory). */
 
 /* x <- fp16(x + delta) (delta NULL: no add); h <- fp16(x * rsqrt(mean(x^2) + eps) * weight).
  * rows x n, n a multiple of 8, pointers 16-byte aligned, strides in elements (multiples of 8). */
 EXL3_API int exl3_add_rmsnorm(uint16_t* x, const uint16_t* delta, const uint16_t* weight, uint16_t* h,
                               int rows, int64_t n, int64_t x_row_stride, int64_t delta_row_stride,
-                              int64_t h_row_stride, float eps, exl3_stream_t stream);
+                              int64_t h_row_stride, float eps, unsigned flags, exl3_stream_t stream);
 
 /* qkv row r = [q_heads | kv_heads | kv_heads] x 128.  q and k get the rotate-half rotary
  * embedding with rows r of cos_table / sin_table (rows x 128); q -> q_out (rows, q_heads, 128),
@@ -213,7 +215,7 @@ EXL3_API int exl3_add_rmsnorm(uint16_t* x, const uint16_t* delta, const uint16_t
 EXL3_API int exl3_rope_append(const uint16_t* qkv, int64_t qkv_row_stride, const uint16_t* cos_table,
                               const uint16_t* sin_table, uint16_t* q_out, uint16_t* k_cache,
                               uint16_t* v_cache, int rows, int q_heads, int kv_heads, int64_t cache_len,
-                              int pos0, exl3_stream_t stream);
+                              int pos0, unsigned flags, exl3_stream_t stream);
 
 /* Grouped-query attention of `rows` (1..16) new positions over caches that already hold them:
  * position r sees keys 0 .. ctx + r.  q (rows, q_heads, 128) -> out (rows, q_heads * 128).
@@ -221,11 +223,11 @@ EXL3_API int exl3_rope_append(const uint16_t* qkv, int64_t qkv_row_stride, const
 EXL3_API size_t exl3_attn_workspace_bytes(int rows, int q_heads, int kv_heads, int64_t total_keys);
 EXL3_API int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache,
                               uint16_t* out, int rows, int q_heads, int kv_heads, int64_t cache_len, int ctx,
-                              void* workspace, size_t workspace_bytes, exl3_stream_t stream);
+                              void* workspace, size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
 
 /* gate_up row = [gate (h) | up (h)]; out = fp16(silu(gate) * up).  h a multiple of 8. */
 EXL3_API int exl3_swiglu(const uint16_t* gate_up, int64_t gu_row_stride, uint16_t* out, int64_t out_row_stride,
-                         int rows, int64_t h, exl3_stream_t stream);
+                         int rows, int64_t h, unsigned flags, exl3_stream_t stream);
 
 /* ---- output exchange over peer memory (tensor parallel by output tile) -------------------
  * The reference is single-device; sharding a linear by output tile (ponyexl3/ref/reconstruct.py:13-23
@@ -252,8 +254,9 @@ EXL3_API int exl3_gemv_peers(const void* x, int x_dtype, int rows, int64_t x_row
                              unsigned flags, exl3_stream_t stream);
 EXL3_API int exl3_peer_allgather(const uint16_t* src, int rows, int64_t cols, int64_t src_row_stride,
                                  const uint64_t* dst_peers, const uint64_t* counter_peers, int n_peers,
-                                 int64_t dst_row_stride, int64_t col0, exl3_stream_t stream);
-EXL3_API int exl3_peer_wait(uint32_t* counter, uint32_t target, void* workspace, exl3_stream_t stream);
+                                 int64_t dst_row_stride, int64_t col0, unsigned flags, exl3_stream_t stream);
+EXL3_API int exl3_peer_wait(uint32_t* counter, uint32_t target, void* workspace, unsigned flags,
+                            exl3_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -53,19 +53,19 @@ _PROTOTYPES = {
                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_uint,
                                   c_void_p]),
     "exl3_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
-                                 c_int64, ctypes.c_float, c_void_p]),
+                                 c_int64, ctypes.c_float, c_uint, c_void_p]),
     "exl3_rope_append": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                 c_int, c_int, c_int64, c_int, c_void_p]),
+                                 c_int, c_int, c_int64, c_int, c_uint, c_void_p]),
     "exl3_attn_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int64]),
     "exl3_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int,
-                                 c_void_p, c_size_t, c_void_p]),
-    "exl3_swiglu": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_void_p]),
+                                 c_void_p, c_size_t, c_uint, c_void_p]),
+    "exl3_swiglu": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_uint, c_void_p]),
     "exl3_gemv_peers": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
                                 c_void_p, c_size_t, c_uint, c_void_p]),
     "exl3_peer_allgather": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64,
-                                    c_int64, c_void_p]),
-    "exl3_peer_wait": (c_int, [c_void_p, c_uint, c_void_p, c_void_p]),
+                                    c_int64, c_uint, c_void_p]),
+    "exl3_peer_wait": (c_int, [c_void_p, c_uint, c_void_p, c_uint, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

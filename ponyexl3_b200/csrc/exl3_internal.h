@@ -13,6 +13,25 @@ int device_sm_count();              // SM count of the current device (cached pe
 int note_cuda(cudaError_t e);       // records the error text; returns EXL3_OK or EXL3_E_CUDA
 int check_launch();                 // note_cuda(cudaGetLastError())
 
+// Launch with or without the programmatic-dependent-launch attribute (EXL3_FLAG_PDL): the kernel
+// may then start while its predecessor in the stream drains; it orders itself with griddep_wait.
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl,
+                         Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return note_cuda(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
+}
+
 // ---- workspace layout ------------------------------------------------------------------------
 // [0, 256)      status word + padding (zero = no bounded wait ever gave up)
 // [256, ...)    scratch: the rotated activations xh of the current call — one 32-bit word per

@@ -68,18 +68,21 @@ __global__ void __launch_bounds__(512) peer_allgather_kernel(const PeerCopyArgs 
 
 using namespace exl3;
 
-extern "C" int exl3_peer_wait(uint32_t* counter, uint32_t target, void* workspace, exl3_stream_t stream)
+extern "C" int exl3_peer_wait(uint32_t* counter, uint32_t target, void* workspace, unsigned flags,
+                              exl3_stream_t stream)
 {
     if (!counter || !workspace) return EXL3_E_NULL;
     if (target == 0) return EXL3_E_RANGE;
-    peer_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(counter, target,
-                                                       reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kWsStatus));
-    return check_launch();
+    // With EXL3_FLAG_PDL the poll is resident while the producing kernel of this rank still runs,
+    // and ends the moment the last block (local or remote) has arrived.
+    return launch_kernel(peer_wait_kernel, dim3(1), dim3(1), 0, (cudaStream_t)stream, (flags & EXL3_FLAG_PDL) != 0,
+                         reinterpret_cast<unsigned*>(counter), (unsigned)target,
+                         reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kWsStatus));
 }
 
 extern "C" int exl3_peer_allgather(const uint16_t* src, int rows, int64_t cols, int64_t src_row_stride,
                                    const uint64_t* dst_peers, const uint64_t* counter_peers, int n_peers,
-                                   int64_t dst_row_stride, int64_t col0, exl3_stream_t stream)
+                                   int64_t dst_row_stride, int64_t col0, unsigned flags, exl3_stream_t stream)
 {
     if (!src || !dst_peers || !counter_peers) return EXL3_E_NULL;
     if (n_peers < 1 || n_peers > kMaxPeers) return EXL3_E_RANGE;
@@ -100,6 +103,6 @@ extern "C" int exl3_peer_allgather(const uint16_t* src, int rows, int64_t cols, 
         a.dst[p] = reinterpret_cast<__half*>(dst_peers[p]);
         a.ctr[p] = reinterpret_cast<unsigned*>(counter_peers[p]);
     }
-    peer_allgather_kernel<<<1, 512, 0, (cudaStream_t)stream>>>(a);
-    return check_launch();
+    return launch_kernel(peer_allgather_kernel, dim3(1), dim3(512), 0, (cudaStream_t)stream,
+                         (flags & EXL3_FLAG_PDL) != 0, a);
 }

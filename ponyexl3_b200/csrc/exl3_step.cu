@@ -325,29 +325,42 @@ __global__ void __launch_bounds__(NW * 32) attn_partial_kernel(const AttnArgs a)
 }
 
 // out[r, head, :] = sum_i 2^(m_i - m*) O_i / sum_i 2^(m_i - m*) l_i over the chunks i.
-__global__ void __launch_bounds__(128) attn_combine_kernel(const AttnArgs a)
+// 128 features x 4 chunk lanes per CTA: lane j takes chunks j, j + 4, ... so the loads of the
+// (up to a few dozen) chunks are in flight together instead of one after the other.
+__global__ void __launch_bounds__(512) attn_combine_kernel(const AttnArgs a)
 {
     griddep_launch_dependents();
     griddep_wait();
-    const int m = blockIdx.x, kvh = blockIdx.y, d = threadIdx.x;
+    __shared__ float s_acc[4][128], s_l[4], s_m[4];
+    const int m = blockIdx.x, kvh = blockIdx.y, d = threadIdx.x & 127, j = threadIdx.x >> 7;
     const int M = a.group * a.rows;
     const int64_t base = (int64_t)kvh * a.nsplit * M + m;
-    float mmax = -INFINITY;
-    for (int i = 0; i < a.nsplit; i++) mmax = fmaxf(mmax, a.part_ml[(base + (int64_t)i * M) * 2]);
+    float mloc = -INFINITY;
+    for (int i = j; i < a.nsplit; i += 4) mloc = fmaxf(mloc, a.part_ml[(base + (int64_t)i * M) * 2]);
+    if (d == 0) s_m[j] = mloc;
+    __syncthreads();
+    const float mmax = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
     float acc = 0.f, lsum = 0.f;
-    for (int i = 0; i < a.nsplit; i++) {
+#pragma unroll 4
+    for (int i = j; i < a.nsplit; i += 4) {
         const int64_t row = base + (int64_t)i * M;
         const float mi = a.part_ml[row * 2];
-        if (mi == -INFINITY) continue;                  // a chunk this row does not see at all
-        const float w = exp2f(mi - mmax);
+        const float w = mi == -INFINITY ? 0.f : exp2f(mi - mmax);   // a chunk this row does not see
         acc += w * a.part_o[row * 128 + d];
         lsum += w * a.part_ml[row * 2 + 1];
     }
-    const int gq = m / a.rows, r = m - gq * a.rows;
-    a.out[((int64_t)r * a.hq + kvh * a.group + gq) * 128 + d] = __float2half_rn(acc / lsum);
+    s_acc[j][d] = acc;
+    if (d == 0) s_l[j] = lsum;
+    __syncthreads();
+    if (j == 0) {
+        const float num = s_acc[0][d] + s_acc[1][d] + s_acc[2][d] + s_acc[3][d];
+        const float den = s_l[0] + s_l[1] + s_l[2] + s_l[3];
+        const int gq = m / a.rows, r = m - gq * a.rows;
+        a.out[((int64_t)r * a.hq + kvh * a.group + gq) * 128 + d] = __float2half_rn(num / den);
+    }
 }
 
-template <int NW> static int launch_attn_partial(const AttnArgs& a, cudaStream_t s)
+template <int NW> static int launch_attn_partial(const AttnArgs& a, cudaStream_t s, bool pdl)
 {
     const size_t smem = 4 * (size_t)kAttnTileBytes;
     static bool set[16] = {};
@@ -359,8 +372,8 @@ template <int NW> static int launch_attn_partial(const AttnArgs& a, cudaStream_t
         if (e != cudaSuccess) return note_cuda(e);
         set[dev] = true;
     }
-    attn_partial_kernel<NW><<<dim3((unsigned)a.nsplit, (unsigned)a.hkv), NW * 32, smem, s>>>(a);
-    return check_launch();
+    return launch_kernel(attn_partial_kernel<NW>, dim3((unsigned)a.nsplit, (unsigned)a.hkv), dim3(NW * 32), smem, s,
+                         pdl, a);
 }
 
 // Chunking: about two CTAs per SM, chunks a multiple of the 64-key tile.
@@ -380,45 +393,43 @@ using namespace exl3;
 
 extern "C" int exl3_add_rmsnorm(uint16_t* x, const uint16_t* delta, const uint16_t* weight, uint16_t* h,
                                 int rows, int64_t n, int64_t x_row_stride, int64_t delta_row_stride,
-                                int64_t h_row_stride, float eps, exl3_stream_t stream)
+                                int64_t h_row_stride, float eps, unsigned flags, exl3_stream_t stream)
 {
     if (!x || !weight || !h) return EXL3_E_NULL;
     if (rows < 1 || n < 8 || n % 8) return EXL3_E_SHAPE;
     if (x_row_stride % 8 || h_row_stride % 8 || (delta && delta_row_stride % 8)) return EXL3_E_ALIGN;
     if (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)h | (uintptr_t)delta) & 15) return EXL3_E_ALIGN;
-    add_rmsnorm_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<__half*>(x), reinterpret_cast<const __half*>(delta),
-        reinterpret_cast<const __half*>(weight), reinterpret_cast<__half*>(h), (int)n, x_row_stride,
-        delta_row_stride, h_row_stride, eps);
-    return check_launch();
+    return launch_kernel(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(256), 0, (cudaStream_t)stream,
+                         (flags & EXL3_FLAG_PDL) != 0, reinterpret_cast<__half*>(x),
+                         reinterpret_cast<const __half*>(delta), reinterpret_cast<const __half*>(weight),
+                         reinterpret_cast<__half*>(h), (int)n, x_row_stride, delta_row_stride, h_row_stride, eps);
 }
 
 extern "C" int exl3_rope_append(const uint16_t* qkv, int64_t qkv_row_stride, const uint16_t* cos_table,
                                 const uint16_t* sin_table, uint16_t* q_out, uint16_t* k_cache,
                                 uint16_t* v_cache, int rows, int q_heads, int kv_heads, int64_t cache_len,
-                                int pos0, exl3_stream_t stream)
+                                int pos0, unsigned flags, exl3_stream_t stream)
 {
     if (!qkv || !cos_table || !sin_table || !q_out || !k_cache || !v_cache) return EXL3_E_NULL;
     if (rows < 1 || q_heads < 1 || kv_heads < 1) return EXL3_E_SHAPE;
     if (pos0 < 0 || (int64_t)pos0 + rows > cache_len) return EXL3_E_RANGE;
-    rope_append_kernel<<<dim3((unsigned)rows, (unsigned)(q_heads + 2 * kv_heads)), 64, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const __half*>(qkv), qkv_row_stride, reinterpret_cast<const __half*>(cos_table),
-        reinterpret_cast<const __half*>(sin_table), reinterpret_cast<__half*>(q_out),
-        reinterpret_cast<__half*>(k_cache), reinterpret_cast<__half*>(v_cache), q_heads, kv_heads, cache_len,
-        pos0);
-    return check_launch();
+    return launch_kernel(rope_append_kernel, dim3((unsigned)rows, (unsigned)(q_heads + 2 * kv_heads)), dim3(64), 0,
+                         (cudaStream_t)stream, (flags & EXL3_FLAG_PDL) != 0, reinterpret_cast<const __half*>(qkv),
+                         qkv_row_stride, reinterpret_cast<const __half*>(cos_table),
+                         reinterpret_cast<const __half*>(sin_table), reinterpret_cast<__half*>(q_out),
+                         reinterpret_cast<__half*>(k_cache), reinterpret_cast<__half*>(v_cache), q_heads, kv_heads,
+                         cache_len, pos0);
 }
 
 extern "C" int exl3_swiglu(const uint16_t* gate_up, int64_t gu_row_stride, uint16_t* out, int64_t out_row_stride,
-                           int rows, int64_t h, exl3_stream_t stream)
+                           int rows, int64_t h, unsigned flags, exl3_stream_t stream)
 {
     if (!gate_up || !out) return EXL3_E_NULL;
     if (rows < 1 || h < 8 || h % 8) return EXL3_E_SHAPE;
     if (gu_row_stride % 8 || out_row_stride % 8 || (((uintptr_t)gate_up | (uintptr_t)out) & 15)) return EXL3_E_ALIGN;
-    swiglu_kernel<<<dim3((unsigned)((h / 8 + 255) / 256), (unsigned)rows), 256, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const __half*>(gate_up), gu_row_stride, reinterpret_cast<__half*>(out), out_row_stride,
-        (int)h);
-    return check_launch();
+    return launch_kernel(swiglu_kernel, dim3((unsigned)((h / 8 + 255) / 256), (unsigned)rows), dim3(256), 0,
+                         (cudaStream_t)stream, (flags & EXL3_FLAG_PDL) != 0, reinterpret_cast<const __half*>(gate_up),
+                         gu_row_stride, reinterpret_cast<__half*>(out), out_row_stride, (int)h);
 }
 
 extern "C" size_t exl3_attn_workspace_bytes(int rows, int q_heads, int kv_heads, int64_t total_keys)
@@ -432,7 +443,7 @@ extern "C" size_t exl3_attn_workspace_bytes(int rows, int q_heads, int kv_heads,
 
 extern "C" int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache,
                                 uint16_t* out, int rows, int q_heads, int kv_heads, int64_t cache_len, int ctx,
-                                void* workspace, size_t workspace_bytes, exl3_stream_t stream)
+                                void* workspace, size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
 {
     if (!q || !k_cache || !v_cache || !out || !workspace) return EXL3_E_NULL;
     if (rows < 1 || rows > 16) return EXL3_E_ROWS;
@@ -456,18 +467,18 @@ extern "C" int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, cons
     a.part_ml = a.part_o + (size_t)kv_heads * a.nsplit * m * 128;
     a.scale_log2 = 1.4426950408889634f * 0.08838834764831845f;   // log2(e) / sqrt(128)
     cudaStream_t s = (cudaStream_t)stream;
+    const bool pdl = (flags & EXL3_FLAG_PDL) != 0;
     int rc;
     switch ((m + 15) / 16) {
-        case 1: rc = launch_attn_partial<1>(a, s); break;
-        case 2: rc = launch_attn_partial<2>(a, s); break;
-        case 3: rc = launch_attn_partial<3>(a, s); break;
-        case 4: rc = launch_attn_partial<4>(a, s); break;
-        case 5: rc = launch_attn_partial<5>(a, s); break;
-        case 6: rc = launch_attn_partial<6>(a, s); break;
-        case 7: rc = launch_attn_partial<7>(a, s); break;
-        default: rc = launch_attn_partial<8>(a, s); break;
+        case 1: rc = launch_attn_partial<1>(a, s, pdl); break;
+        case 2: rc = launch_attn_partial<2>(a, s, pdl); break;
+        case 3: rc = launch_attn_partial<3>(a, s, pdl); break;
+        case 4: rc = launch_attn_partial<4>(a, s, pdl); break;
+        case 5: rc = launch_attn_partial<5>(a, s, pdl); break;
+        case 6: rc = launch_attn_partial<6>(a, s, pdl); break;
+        case 7: rc = launch_attn_partial<7>(a, s, pdl); break;
+        default: rc = launch_attn_partial<8>(a, s, pdl); break;
     }
     if (rc) return rc;
-    attn_combine_kernel<<<dim3((unsigned)m, (unsigned)kv_heads), 128, 0, s>>>(a);
-    return check_launch();
+    return launch_kernel(attn_combine_kernel, dim3((unsigned)m, (unsigned)kv_heads), dim3(512), 0, s, pdl, a);
 }

@@ -92,6 +92,7 @@ class SyntheticDenseDecoder:
         # native_glue: norm / rotary + cache append / attention / SwiGLU through the library's
         # step kernels (head_dim 128 only); otherwise the same math as PyTorch ops
         self.native_glue = native_glue and cfg.head_dim == 128
+        self.pdl_glue = pdl
         self.world = (dist.get_world_size(group)
                       if (tensor_parallel and dist.is_available() and dist.is_initialized()) else 1)
         self.rank = dist.get_rank(group) if self.world > 1 else 0
@@ -252,11 +253,12 @@ class SyntheticDenseDecoder:
         peer = self.peer
         if peer is not None:
             peer.restart()
+        pdl = self.pdl_glue
 
         def gather(t, spans, total):
             if peer is None:
                 return self._gather(t, spans)
-            return ops.peer_allgather(t, exchange=peer, cols_total=total, col0=spans[self.rank][0])
+            return ops.peer_allgather(t, exchange=peer, cols_total=total, col0=spans[self.rank][0], pdl=pdl)
 
         def linear_gather(m, t, spans, total):
             if peer is None:
@@ -268,15 +270,15 @@ class SyntheticDenseDecoder:
         x = self.embed[tokens]                                            # (rows, hidden), updated in place
         delta = None
         for L in self.layers:
-            h = ops.add_rmsnorm(x, delta, L.norm1, c.rms_eps)
+            h = ops.add_rmsnorm(x, delta, L.norm1, c.rms_eps, pdl=pdl)
             qkv = L.qkv.forward_packed(h)
-            q = ops.rope_append(qkv, self.cos, self.sin, L.k_cache, L.v_cache, self.hq, c.context)
-            a = gather(ops.attn_decode(q, L.k_cache, L.v_cache, c.context), head_spans, q_all)
+            q = ops.rope_append(qkv, self.cos, self.sin, L.k_cache, L.v_cache, self.hq, c.context, pdl=pdl)
+            a = gather(ops.attn_decode(q, L.k_cache, L.v_cache, c.context, pdl=pdl), head_spans, q_all)
             o = linear_gather(L.o, a, self.hidden_spans, c.hidden)
-            h = ops.add_rmsnorm(x, o, L.norm2, c.rms_eps)
-            act = gather(ops.swiglu(L.gate_up.forward_packed(h)), self.inter_spans, c.intermediate)
+            h = ops.add_rmsnorm(x, o, L.norm2, c.rms_eps, pdl=pdl)
+            act = gather(ops.swiglu(L.gate_up.forward_packed(h), pdl=pdl), self.inter_spans, c.intermediate)
             delta = linear_gather(L.down, act, self.hidden_spans, c.hidden)
-        h = ops.add_rmsnorm(x, delta, self.final_norm, c.rms_eps)
+        h = ops.add_rmsnorm(x, delta, self.final_norm, c.rms_eps, pdl=pdl)
         return self.head(h)
 
     @torch.no_grad()

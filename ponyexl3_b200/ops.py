@@ -259,8 +259,12 @@ def gemm_tiles(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None,
 
 # ---- the caller's side of a decode step (exl3_step.cu) ---------------------------------------
 
+def _flags(pdl: bool) -> int:
+    return _lib.FLAG_PDL if pdl else 0
+
+
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, pdl: bool = False) -> torch.Tensor:
     """In place x <- x + delta (skipped when delta is None); returns fp16 RMSNorm(x) * weight.
     x, delta (rows, n) fp16 with unit column stride."""
     _need_cuda(x, "x")
@@ -270,13 +274,15 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
         delta = delta.contiguous()
     _lib.check(_lib.load().exl3_add_rmsnorm(
         x.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(), h.data_ptr(), rows, n,
-        x.stride(0), 0 if delta is None else delta.stride(0), h.stride(0), float(eps), _stream(x.device)),
+        x.stride(0), 0 if delta is None else delta.stride(0), h.stride(0), float(eps), _flags(pdl),
+        _stream(x.device)),
         "exl3_add_rmsnorm")
     return h
 
 
 def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_cache: torch.Tensor,
-                v_cache: torch.Tensor, q_heads: int, pos0: int, out: torch.Tensor | None = None) -> torch.Tensor:
+                v_cache: torch.Tensor, q_heads: int, pos0: int, out: torch.Tensor | None = None,
+                pdl: bool = False) -> torch.Tensor:
     """qkv (rows, (q_heads + 2 kv_heads) * 128) -> rotated q (rows, q_heads, 128); rotated k and
     v are written to rows pos0.. of the caches (kv_heads, cache_len, 128)."""
     _need_cuda(qkv, "qkv")
@@ -287,7 +293,7 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_cache
     q = out if out is not None else torch.empty((rows, q_heads, 128), dtype=torch.float16, device=qkv.device)
     _lib.check(_lib.load().exl3_rope_append(
         qkv.data_ptr(), qkv.stride(0), cos.data_ptr(), sin.data_ptr(), q.data_ptr(), k_cache.data_ptr(),
-        v_cache.data_ptr(), rows, q_heads, kv_heads, cache_len, int(pos0), _stream(qkv.device)),
+        v_cache.data_ptr(), rows, q_heads, kv_heads, cache_len, int(pos0), _flags(pdl), _stream(qkv.device)),
         "exl3_rope_append")
     return q
 
@@ -296,7 +302,7 @@ _attn_ws: dict[int, torch.Tensor] = {}
 
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx: int,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, pdl: bool = False) -> torch.Tensor:
     """q (rows, q_heads, 128) over caches (kv_heads, cache_len, 128) that already hold the new
     positions ctx .. ctx+rows-1 -> (rows, q_heads * 128); position r sees keys 0 .. ctx + r."""
     _need_cuda(q, "q")
@@ -316,18 +322,18 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, c
     y = out if out is not None else torch.empty((rows, q_heads * 128), dtype=torch.float16, device=q.device)
     _lib.check(lib.exl3_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), y.data_ptr(), rows,
                                     q_heads, kv_heads, cache_len, int(ctx), ws.data_ptr(), ws.numel(),
-                                    _stream(q.device)), "exl3_attn_decode")
+                                    _flags(pdl), _stream(q.device)), "exl3_attn_decode")
     return y
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, pdl: bool = False) -> torch.Tensor:
     """gate_up (rows, 2h) = [gate | up] -> fp16 silu(gate) * up, (rows, h)."""
     _need_cuda(gate_up, "gate_up")
     rows, two_h = gate_up.shape
     h = two_h // 2
     y = out if out is not None else torch.empty((rows, h), dtype=torch.float16, device=gate_up.device)
     _lib.check(_lib.load().exl3_swiglu(gate_up.data_ptr(), gate_up.stride(0), y.data_ptr(), y.stride(0), rows, h,
-                                       _stream(gate_up.device)), "exl3_swiglu")
+                                       _flags(pdl), _stream(gate_up.device)), "exl3_swiglu")
     return y
 
 
@@ -353,12 +359,12 @@ def gemv_peers(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh, s
         x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out, k, int(cb),
         ptr(suh), ptr(svh), ptr(bias), y_ptrs, c_ptrs, exchange.world, out_features_total, int(col0),
         ws.buf.data_ptr(), ws.nbytes, _lib.FLAG_PDL if pdl else 0, _stream(x2d.device)), "exl3_gemv_peers")
-    _lib.check(lib.exl3_peer_wait(my_ctr, out_features_total // 128, ws.buf.data_ptr(), _stream(x2d.device)),
-               "exl3_peer_wait")
+    _lib.check(lib.exl3_peer_wait(my_ctr, out_features_total // 128, ws.buf.data_ptr(), _flags(pdl),
+                                  _stream(x2d.device)), "exl3_peer_wait")
     return view
 
 
-def peer_allgather(y_local: torch.Tensor, *, exchange, cols_total: int, col0: int) -> torch.Tensor:
+def peer_allgather(y_local: torch.Tensor, *, exchange, cols_total: int, col0: int, pdl: bool = False) -> torch.Tensor:
     """(rows, local) slice -> this rank's complete (rows, cols_total) row, over peer memory."""
     _need_cuda(y_local, "y_local")
     rows, cols = y_local.shape
@@ -368,8 +374,8 @@ def peer_allgather(y_local: torch.Tensor, *, exchange, cols_total: int, col0: in
     ws = Workspace.get(y_local.device, 1, 128)
     _, y_ptrs, c_ptrs, view, my_ctr = exchange.take(rows, cols_total)
     _lib.check(lib.exl3_peer_allgather(y_local.data_ptr(), rows, cols, y_local.stride(0), y_ptrs, c_ptrs,
-                                       exchange.world, cols_total, int(col0), _stream(y_local.device)),
+                                       exchange.world, cols_total, int(col0), _flags(pdl), _stream(y_local.device)),
                "exl3_peer_allgather")
-    _lib.check(lib.exl3_peer_wait(my_ctr, exchange.world, ws.buf.data_ptr(), _stream(y_local.device)),
+    _lib.check(lib.exl3_peer_wait(my_ctr, exchange.world, ws.buf.data_ptr(), _flags(pdl), _stream(y_local.device)),
                "exl3_peer_wait")
     return view

@@ -53,7 +53,7 @@ def test_gemv_peers_single_peer_equals_gemv(lib, rows, k):
                              suh.data_ptr(), svh.data_ptr(), None, _u64(y_full.data_ptr()), _u64(ctr.data_ptr()),
                              1, full, col0, ws.data_ptr(), n, 0, st)
     assert rc == 0
-    assert lib.exl3_peer_wait(ctr.data_ptr(), outf // 128, ws.data_ptr(), st) == 0
+    assert lib.exl3_peer_wait(ctr.data_ptr(), outf // 128, ws.data_ptr(), 0, st) == 0
     torch.cuda.synchronize()
     assert _status(lib, ws) == 0
     assert int(ctr[0]) == 0                                     # re-armed by the waiter
@@ -70,8 +70,8 @@ def test_peer_allgather_single_peer(lib):
     ws, _ = _private_ws()
     st = torch.cuda.current_stream().cuda_stream
     assert lib.exl3_peer_allgather(src.data_ptr(), rows, cols, src.stride(0), _u64(dst.data_ptr()),
-                                   _u64(ctr.data_ptr()), 1, full, col0, st) == 0
-    assert lib.exl3_peer_wait(ctr.data_ptr(), 1, ws.data_ptr(), st) == 0
+                                   _u64(ctr.data_ptr()), 1, full, col0, 0, st) == 0
+    assert lib.exl3_peer_wait(ctr.data_ptr(), 1, ws.data_ptr(), 0, st) == 0
     torch.cuda.synchronize()
     assert _status(lib, ws) == 0 and int(ctr[0]) == 0
     assert torch.equal(dst[:, col0:col0 + cols], src) and float(dst[:, :col0].abs().sum()) == 0
@@ -85,7 +85,7 @@ def test_peer_wait_gives_up_and_reports(lib):
     ws, _ = _private_ws()
     st = torch.cuda.current_stream().cuda_stream
     t0 = time.perf_counter()
-    assert lib.exl3_peer_wait(ctr.data_ptr(), 1, ws.data_ptr(), st) == 0
+    assert lib.exl3_peer_wait(ctr.data_ptr(), 1, ws.data_ptr(), 0, st) == 0
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     assert _status(lib, ws) & 16
@@ -97,8 +97,8 @@ def test_peer_entry_points_validate(lib):
     ws, n = _private_ws()
     st = torch.cuda.current_stream().cuda_stream
     ctr = torch.zeros(4, dtype=torch.int32, device="cuda")
-    assert lib.exl3_peer_wait(None, 1, ws.data_ptr(), st) == -1            # EXL3_E_NULL
-    assert lib.exl3_peer_wait(ctr.data_ptr(), 0, ws.data_ptr(), st) != 0   # zero arrivals make no sense
+    assert lib.exl3_peer_wait(None, 1, ws.data_ptr(), 0, st) == -1            # EXL3_E_NULL
+    assert lib.exl3_peer_wait(ctr.data_ptr(), 0, ws.data_ptr(), 0, st) != 0   # zero arrivals make no sense
     src = torch.zeros((1, 64), dtype=torch.float16, device="cuda")
     assert lib.exl3_peer_allgather(src.data_ptr(), 1, 64, 64, _u64(src.data_ptr()), _u64(ctr.data_ptr()), 9, 64, 0,
-                                   st) != 0                               # more than 8 peers
+                                   0, st) != 0                               # more than 8 peers
