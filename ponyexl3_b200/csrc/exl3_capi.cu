@@ -81,6 +81,7 @@ int device_sm_count()
 }
 
 void gemv_set_tuning(int ctas_per_sm, int smem_budget_bytes);
+void gemv_force_split(int ksplit);
 
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
@@ -473,6 +474,12 @@ int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh
 EXL3_API void exl3_tune_gemv(int ctas_per_sm, int smem_budget_bytes)
 {
     gemv_set_tuning(ctas_per_sm, smem_budget_bytes);
+}
+
+/* Same kind of hook: force the k-split (CTAs per cluster) of the streamed GEMV; 0 = automatic. */
+EXL3_API void exl3_tune_gemv_split(int ksplit)
+{
+    gemv_force_split(ksplit);
 }
 
 }  // extern "C"

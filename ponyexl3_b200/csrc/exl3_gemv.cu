@@ -23,6 +23,9 @@ void gemv_set_tuning(int ctas_per_sm, int smem_budget_bytes)
         for (int& v : row) v = 0;
 }
 
+static int g_force_split = 0;
+void gemv_force_split(int ksplit) { g_force_split = (ksplit >= 1 && ksplit <= 8) ? ksplit : 0; }
+
 int gemv_active_clusters_probe(int cluster, int smem_bytes);   // exl3_gemv_k4.cu
 
 // Clusters of s CTAs that are resident at once (a cluster must fit inside one GPC, so this
@@ -52,7 +55,9 @@ void gemv_choose_split(int ncb, int nkb, int rows, int* ksplit, int* grid)
     int best_s = 1, best_clusters = 1;
     long best_t = -1;
     const int s_max = std::min(std::min(8, nkb), 1 + 24576 / (rows * 512));
-    for (int s = 1; s <= s_max; s++) {
+    const int s_lo = g_force_split ? std::min(g_force_split, s_max) : 1;
+    const int s_hi = g_force_split ? s_lo : s_max;
+    for (int s = s_lo; s <= s_hi; s++) {
         const int clusters = std::min(ncb, active_clusters(s));
         const long waves = (ncb + clusters - 1) / clusters;
         const long t = waves * ((nkb + s - 1) / s) * 16 + s;   // + s: cost of gathering s partial sums
