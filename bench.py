@@ -624,6 +624,118 @@ def run_decode(args):
         finish_ranks(dist)
 
 
+def run_moe(args):
+    """BASELINE.json configs[3]: stacked-expert SwitchGLU, 256 experts, top-8, hidden 2048, expert
+    intermediate 512, K=4, router logits N(0,1) -> softmax top-8, for --tokens 1, 16 or 4096.
+    N > 1: experts partitioned by expert; few tokens are replicated and the partial outputs summed
+    (all-reduce), many tokens are partitioned and their rows exchanged with two all-to-alls.
+    A step = one SwitchGLU forward (expert outputs before the router-weighted sum)."""
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import datetime
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+    from ponyexl3_b200 import ops
+    from ponyexl3_b200.moe import EXL3SwitchGLU, route_topk
+    from ponyexl3_b200.parallel import (EPSwitchGLU, dispatch_rows_to_experts, return_rows_to_tokens,
+                                        shard_expert_weights)
+
+    E, D, H, kk, k, T = 256, 2048, 512, 8, 4, args.tokens
+    g = torch.Generator(device=dev)
+    g.manual_seed(4000)                                   # the same experts and tokens on every rank
+    ri = lambda *sh: torch.randint(-32768, 32767, sh, dtype=torch.int16, device=dev, generator=g)
+    sg = lambda *sh: (torch.randint(0, 2, sh, device=dev, generator=g) * 2 - 1).to(torch.float16)
+    w = dict(gu_trellis=ri(D // 16, E * 2 * H // 16, 16 * k), gu_suh=sg(E, 2, D), gu_svh=sg(E, 2 * H),
+             dn_trellis=ri(H // 16, E * D // 16, 16 * k), dn_suh=sg(E, H), dn_svh=sg(E, D))
+    x = (torch.randn((T, D), device=dev, generator=g) * 0.02).to(torch.float16)
+    inds, _ = route_topk(torch.randn((1, T, E), device=dev, generator=g), kk)
+    inds = inds.reshape(T, kk)
+    if world == 1:
+        switch = EXL3SwitchGLU(**w, k=k, cb=0)
+        step = lambda: switch(x.view(1, T, D), inds.view(1, T, kk))
+        mode = "single GPU"
+    else:
+        local_sw = EXL3SwitchGLU(**shard_expert_weights(w, E, world, rank), k=k, cb=0)
+        del w
+        if T <= 16:
+            ep = EPSwitchGLU(local_sw, E)
+            step = lambda: ep(x.view(1, T, D), inds.view(1, T, kk))
+            mode = f"ep{world}: tokens replicated, all-reduce of partial outputs"
+        else:
+            t0, t1 = T * rank // world, T * (rank + 1) // world
+            xl, il = x[t0:t1].contiguous(), inds[t0:t1].contiguous()
+
+            def step():
+                rows, e_local, book = dispatch_rows_to_experts(xl, il, E)
+                if rows.shape[0]:
+                    yr = local_sw(rows.reshape(1, -1, D), e_local.reshape(1, -1, 1)).reshape(-1, D)
+                else:
+                    yr = torch.empty((0, D), dtype=torch.float16, device=dev)
+                return return_rows_to_tokens(yr, book)
+            mode = f"ep{world}: tokens partitioned, two all-to-alls"
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    status = ops.Workspace.get(dev, 1, 128).status()
+    if rank == 0:
+        touched = int(torch.unique(inds).numel())
+        packed = touched * 3 * D * H * k // 8
+        flops = 2.0 * T * kk * 3 * D * H
+        hbm_peak, kind = measured_peaks()
+        few = T <= 16
+        line = {
+            "metric": "moe_expert_weight_bandwidth" if few else "moe_expert_tflops",
+            "value": packed / (ms * 1e-3) / 1e9 if few else flops / (ms * 1e-3) / 1e12,
+            "unit": "GB/s" if few else "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"configs[3]: SwitchGLU, {E} experts, top-{kk}, hidden {D}, intermediate {H}, "
+                                   f"K={k}, {T} tokens", "tokens": T, "experts_touched": touched,
+                       "packed_bytes_touched": packed, "flops": flops, "parallelism": mode,
+                       "launch": "eager (expert tables are built on the device every call)"},
+            "roofline": ({"bound": "hbm", "achieved": packed / (ms * 1e-3) / 1e9 / world, "peak": hbm_peak,
+                          "unit": "GB/s", "frac": packed / (ms * 1e-3) / 1e9 / world / hbm_peak, "traffic": None,
+                          "peak_kind": f"of {kind}"} if few else
+                         {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12 / world, "peak": 1657.8,
+                          "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / world / 1657.8, "traffic": None,
+                          "peak_kind": "of measured (burst)"}),
+            "cpu_baseline": None, "e2e": None, "clocks": clocks, "kernel_status": status,
+        }
+        emit(line)
+    if dist is not None:
+        finish_ranks(dist)
+
+
 def run_sweep(args):
     """BASELINE.json configs[1] in full: rows x K x codebook x shape, one graph-captured train
     of launches over distinct layers (more packed bytes than L2) per case.  Prints one JSON
@@ -749,8 +861,10 @@ def main():
     ap.add_argument("--sweep-cb", default="0,1,2")
     ap.add_argument("--sweep-iters", type=int, default=5)
     ap.add_argument("--sweep-out", default=None, help="write a markdown table of the sweep here")
-    ap.add_argument("--workload", choices=["gemv", "decode"], default="gemv",
-                    help="gemv = the headline batch-1 GEMV ring; decode = the 64-layer decode step")
+    ap.add_argument("--workload", choices=["gemv", "decode", "moe"], default="gemv",
+                    help="gemv = the headline batch-1 GEMV ring; decode = the 64-layer decode step; "
+                         "moe = the 256-expert SwitchGLU layer")
+    ap.add_argument("--tokens", type=int, default=1, help="moe workload: tokens per step (1, 16, 4096)")
     ap.add_argument("--rows", type=int, default=1, help="decode workload: new positions per step (1 or 16)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: transformer layers")
     args = ap.parse_args()
@@ -766,6 +880,8 @@ def main():
         run_reference(args)
     elif args.workload == "decode":
         run_decode(args)
+    elif args.workload == "moe":
+        run_moe(args)
     else:
         run_gpu(args)
 
