@@ -258,6 +258,22 @@ EXL3_API int exl3_peer_allgather(const uint16_t* src, int rows, int64_t cols, in
 EXL3_API int exl3_peer_wait(uint32_t* counter, uint32_t target, void* workspace, unsigned flags,
                             exl3_stream_t stream);
 
+/* ---- stacked-expert SwitchGLU, decode-class calls -------------------------------------------
+ * Builds, on the device, the tables exl3_gemv_blocks takes for the two launches of a
+ * SwitchGLU call with few tokens (the reference maps (token, slot) pairs to experts for its
+ * mapped GEMV in the same way, ponyexl3/mlx/exl3_moe.py:634-683).  indices: n_pairs expert ids
+ * (int32 or int64: index_bytes 4 or 8), pair s = token s / top_k.  Stacked layouts as in the
+ * reference: gu_trellis (d/16, E*2*h/16, 16K) = all gates then all ups, gu_suh (E*2, d),
+ * gu_svh (E, 2h), dn_trellis (h/16, E*d/16, 16K), dn_suh (E, h), dn_svh (E, d).
+ *   blocks_gu (n_pairs*2*h/128, 4), row_src_gu (2*n_pairs), suh_row_gu (2*n_pairs): the gate/up
+ *     launch over 2*n_pairs rotated rows (row 2s+p = pair s, p = 0 gate / 1 up), output
+ *     (n_pairs, 2h) = [gate | up] per pair;
+ *   blocks_dn (n_pairs*d/128, 4), suh_row_dn (n_pairs): the down launch, output (n_pairs, d). */
+EXL3_API int exl3_moe_decode_tables(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                    int num_experts, int64_t d, int64_t h, int32_t* blocks_gu,
+                                    int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* blocks_dn,
+                                    int32_t* suh_row_dn, unsigned flags, exl3_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -66,6 +66,8 @@ _PROTOTYPES = {
     "exl3_peer_allgather": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64,
                                     c_int64, c_uint, c_void_p]),
     "exl3_peer_wait": (c_int, [c_void_p, c_uint, c_void_p, c_uint, c_void_p]),
+    "exl3_moe_decode_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

@@ -1,0 +1,85 @@
+// Launch tables of the stacked-expert SwitchGLU for decode-class calls (few tokens): every
+// (token, slot) pair is a one-row problem against its expert's column range of the stacked
+// trellises (the reference maps pairs to experts the same way for its mapped GEMV,
+// ponyexl3/mlx/exl3_moe.py:634-683).  One kernel turns the routing indices into the block
+// tables and row maps that exl3_gemv_blocks takes for the gate/up launch and the down launch,
+// so a call is a handful of launches with no host round trip.
+#include <algorithm>
+
+#include "exl3_internal.h"
+
+namespace exl3 {
+
+struct MoeTableArgs {
+    const void* indices;   // (n,) expert of every (token, slot) pair, int32 or int64
+    int idx64;
+    int n, kk, E, D, H;
+    int32_t* blocks_gu;    // (n * 2 * H/128, 4): phys, xrow, sv_off, y_off
+    int32_t* row_src_gu;   // (2n,): token of rotated row 2s + p
+    int32_t* suh_row_gu;   // (2n,): row of gu_suh (E*2, D) for rotated row 2s + p
+    int32_t* blocks_dn;    // (n * D/128, 4)
+    int32_t* suh_row_dn;   // (n,): expert of pair s
+};
+
+__global__ void __launch_bounds__(256) moe_decode_tables_kernel(const MoeTableArgs a)
+{
+    griddep_launch_dependents();
+    griddep_wait();
+    const int gb = a.H / 128, db = a.D / 128;
+    const int n_gu = a.n * 2 * gb, n_dn = a.n * db;
+    auto expert = [&](int s) -> int {
+        const long long e = a.idx64 ? static_cast<const long long*>(a.indices)[s]
+                                    : (long long)static_cast<const int*>(a.indices)[s];
+        return (int)(e < 0 ? 0 : (e >= a.E ? a.E - 1 : e));       // a bad index must not leave the tensors
+    };
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_gu + n_dn; i += gridDim.x * blockDim.x) {
+        if (i < n_gu) {
+            const int j = i % gb, sp = i / gb, p = sp & 1, s = sp >> 1, e = expert(s);
+            int4 b;
+            b.x = (p * a.E + e) * gb + j;                   // all gates, then all ups
+            b.y = 2 * s + p;
+            b.z = e * 2 * a.H + p * a.H + 128 * j;
+            b.w = s * 2 * a.H + p * a.H + 128 * j;
+            reinterpret_cast<int4*>(a.blocks_gu)[i] = b;
+            if (j == 0) {
+                a.row_src_gu[sp] = s / a.kk;
+                a.suh_row_gu[sp] = 2 * e + p;
+            }
+        } else {
+            const int t = i - n_gu, j = t % db, s = t / db, e = expert(s);
+            int4 b;
+            b.x = e * db + j;
+            b.y = s;
+            b.z = e * a.D + 128 * j;
+            b.w = s * a.D + 128 * j;
+            reinterpret_cast<int4*>(a.blocks_dn)[t] = b;
+            if (j == 0) a.suh_row_dn[s] = e;
+        }
+    }
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+extern "C" int exl3_moe_decode_tables(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                      int num_experts, int64_t d, int64_t h, int32_t* blocks_gu,
+                                      int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* blocks_dn,
+                                      int32_t* suh_row_dn, unsigned flags, exl3_stream_t stream)
+{
+    if (!indices || !blocks_gu || !row_src_gu || !suh_row_gu || !blocks_dn || !suh_row_dn) return EXL3_E_NULL;
+    if (index_bytes != 4 && index_bytes != 8) return EXL3_E_DTYPE;
+    if (n_pairs < 1 || top_k < 1 || num_experts < 1 || d < 128 || h < 128 || d % 128 || h % 128)
+        return EXL3_E_SHAPE;
+    if ((int64_t)n_pairs * (2 * h / 128 + d / 128) > (1 << 28)) return EXL3_E_RANGE;
+    if (((uintptr_t)blocks_gu | (uintptr_t)blocks_dn) & 15) return EXL3_E_ALIGN;
+    MoeTableArgs a;
+    a.indices = indices;
+    a.idx64 = index_bytes == 8;
+    a.n = n_pairs; a.kk = top_k; a.E = num_experts; a.D = (int)d; a.H = (int)h;
+    a.blocks_gu = blocks_gu; a.row_src_gu = row_src_gu; a.suh_row_gu = suh_row_gu;
+    a.blocks_dn = blocks_dn; a.suh_row_dn = suh_row_dn;
+    const int total = n_pairs * (int)(2 * h / 128 + d / 128);
+    return launch_kernel(moe_decode_tables_kernel, dim3((unsigned)std::min(1024, (total + 255) / 256)), dim3(256), 0,
+                         (cudaStream_t)stream, (flags & EXL3_FLAG_PDL) != 0, a);
+}

@@ -70,41 +70,41 @@ class EXL3SwitchGLU(torch.nn.Module):
 
     # ---- decode: every (token, slot) pair is a one-row problem -------------------------------
     def _decode(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        """Five launches: tables, rotation + GEMV over (pair, gate|up) blocks, GLU, rotation +
+        GEMV over (pair, down) blocks.  No host round trip, so the call can be captured."""
+        from . import _lib
         E, D, H = self.num_experts, self.input_dims, self.hidden_dims
         R, kk = indices.shape
         n = R * kk
         dev = x2d.device
-        sel = indices.reshape(-1).to(torch.int32)                    # expert of slot s
-        slot = torch.arange(n, device=dev, dtype=torch.int32)
-        tok = slot // kk
-
-        # gate + up: rotated row 2s+p = had(x[tok(s)] * gu_suh[e_s, p]); block (s, p, j)
         gb, db = H // 128, D // 128
-        p = torch.arange(2, device=dev, dtype=torch.int32).view(1, 2, 1)
-        j = torch.arange(gb, device=dev, dtype=torch.int32).view(1, 1, gb)
-        s3, e3 = slot.view(n, 1, 1), sel.view(n, 1, 1)
-        phys = (p * E + e3) * gb + j
-        xrow = (2 * s3 + p).expand(n, 2, gb)
-        sv = e3 * (2 * H) + p * H + 128 * j
-        yo = s3 * (2 * H) + p * H + 128 * j
-        blocks = torch.stack([phys, xrow, sv, yo], dim=-1).reshape(-1, 4).contiguous()
-        row_src = tok.repeat_interleave(2)
-        suh_row = (sel.view(n, 1) * 2 + torch.arange(2, device=dev, dtype=torch.int32)).reshape(-1)
-        ygu = torch.empty(n * 2 * H, dtype=torch.float16, device=dev)
-        ops.gemv_blocks(x2d, xh_rows=2 * n, row_src=row_src.contiguous(), suh=self._gu_suh,
-                        suh_row=suh_row.contiguous(), trellis=self._gu_trellis, k=self.k, cb=self.cb,
-                        blocks=blocks, rows=1, svh=self._gu_svh, bias=None, y=ygu, pdl=self.pdl)
-        ygu = ygu.view(n, 2 * H)
-        h = glu(ygu[:, :H], ygu[:, H:], self.activation)
+        idx = indices.reshape(-1)
+        if idx.dtype not in (torch.int32, torch.int64):
+            idx = idx.to(torch.int64)
+        idx = idx.contiguous()
+        # one int32 buffer: blocks_gu | blocks_dn | row_src_gu | suh_row_gu | suh_row_dn
+        n_gu, n_dn = n * 2 * gb * 4, n * db * 4
+        tab = torch.empty(n_gu + n_dn + 5 * n, dtype=torch.int32, device=dev)
+        blocks_gu, blocks_dn = tab[:n_gu].view(-1, 4), tab[n_gu:n_gu + n_dn].view(-1, 4)
+        o = n_gu + n_dn
+        row_src, suh_row, sel = tab[o:o + 2 * n], tab[o + 2 * n:o + 4 * n], tab[o + 4 * n:o + 5 * n]
+        flags = _lib.FLAG_PDL if self.pdl else 0
+        _lib.check(_lib.load().exl3_moe_decode_tables(
+            idx.data_ptr(), idx.element_size(), n, kk, E, D, H, blocks_gu.data_ptr(), row_src.data_ptr(),
+            suh_row.data_ptr(), blocks_dn.data_ptr(), sel.data_ptr(), flags,
+            torch.cuda.current_stream(dev).cuda_stream), "exl3_moe_decode_tables")
 
-        # down: rotated row s = had(h[s] * dn_suh[e_s]); block (s, j)
-        jd = torch.arange(db, device=dev, dtype=torch.int32).view(1, db)
-        s2, e2 = slot.view(n, 1), sel.view(n, 1)
-        blocks = torch.stack([e2 * db + jd, s2.expand(n, db), e2 * D + 128 * jd, s2 * D + 128 * jd],
-                             dim=-1).reshape(-1, 4).contiguous()
-        y = torch.empty(n * D, dtype=torch.float16, device=dev)
-        ops.gemv_blocks(h, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=sel.contiguous(),
-                        trellis=self._dn_trellis, k=self.k, cb=self.cb, blocks=blocks, rows=1,
+        ygu = torch.empty((n, 2 * H), dtype=torch.float16, device=dev)
+        ops.gemv_blocks(x2d, xh_rows=2 * n, row_src=row_src, suh=self._gu_suh, suh_row=suh_row,
+                        trellis=self._gu_trellis, k=self.k, cb=self.cb, blocks=blocks_gu, rows=1,
+                        svh=self._gu_svh, bias=None, y=ygu, pdl=self.pdl)
+        if self.activation == "silu":
+            h = ops.swiglu(ygu, pdl=self.pdl)
+        else:
+            h = glu(ygu[:, :H], ygu[:, H:], self.activation)
+        y = torch.empty((n, D), dtype=torch.float16, device=dev)
+        ops.gemv_blocks(h, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=sel,
+                        trellis=self._dn_trellis, k=self.k, cb=self.cb, blocks=blocks_dn, rows=1,
                         svh=self._dn_svh, bias=None, y=y, pdl=self.pdl)
         return y.view(R, kk, D)
 
