@@ -378,23 +378,31 @@ def run_gpu(args):
         mods.append(m)
     h_in = {inf: torch.randn((ROWS, inf)).to(torch.float16).pin_memory() for inf in xs}
     d_in = {inf: torch.empty_like(xs[inf]) for inf in xs}
-    h_out = [torch.empty((ROWS, m.out_features if dist is None else m.full_out), dtype=torch.float16).pin_memory()
-             for m in mods]
+    # the step's result: every layer's output row, side by side in one device buffer that goes
+    # back to pinned host memory in one copy at the end of the step
+    widths = [m.full_out if dist is not None else m.out_features for m in mods]
+    d_out = torch.empty((ROWS, sum(widths)), dtype=torch.float16, device=dev)
+    h_out = torch.empty((ROWS, sum(widths)), dtype=torch.float16).pin_memory()
+    offs = [0]
+    for wd in widths:
+        offs.append(offs[-1] + wd)
+    d_views = [d_out[:, a:b] for a, b in zip(offs[:-1], offs[1:])]
     h2d = sum(v.numel() * 2 for v in h_in.values())
-    d2h = sum(v.numel() * 2 for v in h_out)
+    d2h = h_out.numel() * 2
 
     def e2e_step():
         for inf in h_in:
             d_in[inf].copy_(h_in[inf], non_blocking=True)
         if dist is None:
-            for m, ho in zip(mods, h_out):
-                ho.copy_(m(d_in[m.in_features]), non_blocking=True)
+            for m, dv in zip(mods, d_views):
+                m(d_in[m.in_features], out=dv)
         else:
             if peer is not None:
                 peer.restart()
-            for L, ho in zip(layers, h_out):
+            for L, dv in zip(layers, d_views):
                 one_layer(L, d_in[L.inf])
-                ho.copy_(L.y_full, non_blocking=True)
+                dv.copy_(L.y_full)
+        h_out.copy_(d_out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = max(3, min(args.steps, 20))

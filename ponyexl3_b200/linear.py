@@ -82,18 +82,22 @@ class EXL3Linear(torch.nn.Module):
         return self.in_features * self.out_features * self.k // 8
 
     @torch.no_grad()
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """`out`: optional (rows, out_features) fp16 CUDA tensor to write into (unit column stride)."""
         in_shape = x.shape
         if in_shape[-1] != self.in_features:
             raise ValueError(f"expected last dim {self.in_features}, got {in_shape[-1]}")
-        x2d = x.reshape(-1, self.in_features)
+        x2d = x if x.ndim == 2 else x.reshape(-1, self.in_features)
         rows = x2d.shape[0]
         if rows == 0:
             return torch.empty(in_shape[:-1] + (self.out_features,), dtype=torch.float16,
                                device=x.device)
+        if out is not None and (out.shape != (rows, self.out_features) or out.dtype != torch.float16
+                                or out.stride(1) != 1):
+            raise ValueError("out must be a (rows, out_features) fp16 tensor with unit column stride")
         if rows <= GEMV_MAX_ROWS:
             y = ops.gemv(x2d, self._trellis, self.k, self.cb, self._suh, self._svh, self._bias,
-                         pdl=self.pdl, fast_accum=self.fast_accum)
+                         pdl=self.pdl, fast_accum=self.fast_accum, out=out)
         else:
-            y = ops.gemm(x2d, self._trellis, self.k, self.cb, self._suh, self._svh, self._bias)
-        return y.reshape(in_shape[:-1] + (self.out_features,))
+            y = ops.gemm(x2d, self._trellis, self.k, self.cb, self._suh, self._svh, self._bias, out=out)
+        return y if x.ndim == 2 else y.reshape(in_shape[:-1] + (self.out_features,))

@@ -59,9 +59,21 @@ class Workspace:
             cls._per_device[idx] = ws
         return ws
 
+    _need: dict[tuple[int, int], int] = {}
+
     @classmethod
     def get(cls, device: torch.device, rows: int, in_features: int) -> "Workspace":
-        return cls.get_bytes(device, int(_lib.load().exl3_workspace_bytes(rows, in_features)))
+        # the size question goes to the library once per (rows, in) and the answer is kept: this
+        # sits on the per-call host path of every decode GEMV
+        key = (rows, in_features)
+        need = cls._need.get(key)
+        if need is None:
+            need = cls._need[key] = int(_lib.load().exl3_workspace_bytes(rows, in_features))
+        idx = device.index
+        ws = cls._per_device.get(idx) if idx is not None else None
+        if ws is not None and ws.nbytes >= need:
+            return ws
+        return cls.get_bytes(device, need)
 
     def status(self) -> int:
         import ctypes
