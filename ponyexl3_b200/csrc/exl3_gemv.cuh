@@ -216,17 +216,19 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         return;
     }
 
-    if (tid == 0) {
-        for (int s = 0; s < ns; s++) {
-            mbar_init(smem_u32(&full[s]), 1);
-            mbar_init(smem_u32(&empty[s]), 4);
+    if (tid < ns) {
+        mbar_init(smem_u32(&full[tid]), 1);
+        mbar_init(smem_u32(&empty[tid]), 4);
+        if (tid == 0) {
+            mbar_init(smem_u32(red_full), (uint32_t)(S > 1 ? S - 1 : 1));
+            mbar_init(smem_u32(red_done), 1);
         }
-        mbar_init(smem_u32(red_full), (uint32_t)(S > 1 ? S - 1 : 1));
-        mbar_init(smem_u32(red_done), 1);
         mbar_fence_init();
     }
     __syncthreads();
-    if (S > 1) cluster_sync_all();   // every CTA's barriers exist before any remote arrive
+    // Every CTA's barriers must exist before a partner arrives on them, which happens only at
+    // the end of a block: arrive here, wait just before the first remote access.
+    if (S > 1) cluster_arrive();
     griddep_launch_dependents();
 
     // ------------------------------------------------------------------ producer ----
@@ -470,6 +472,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
                 for (int q = 0; q < 4; q++) acc[t][m][q] = 0.f;
             }
         named_bar_sync(1, kConsumerThreads);
+        if (S > 1 && cbi == 0) cluster_wait();   // all CTAs of the cluster have set up their barriers
         if (rank != 0) {
             // The landing slots still hold the previous block until the leader says otherwise.
             if (cbi > 0) {
