@@ -702,7 +702,7 @@ def run_moe(args):
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
-        if T <= 16 and not args.no_graph:      # decode-class calls have no host round trip
+        if (T <= 16 or world == 1) and not args.no_graph:      # no host round trip in these paths
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()

@@ -160,15 +160,17 @@ EXL3_API int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_s
  * `tiles` is a device array of n_tiles x {int32 row0, row_end, tn0, sv_off, y_col, ncols,
  * y_row_delta, 0}; a slot with row0 >= row_end is skipped, so the table can be built on the
  * device with a fixed upper bound and no host synchronisation.  Rotated row i =
- * had(x[row_src[i]] * suh[suh_row[i]]) as in exl3_gemv_blocks.
+ * had(x[row_src[i]] * suh[suh_row[i]]) as in exl3_gemv_blocks.  y_row_map (may be NULL): the
+ * y row that computed row r + y_row_delta is stored to — the last projection of a MoE call
+ * writes straight back into (token, slot) order instead of sorted order.
  * Replaces the segmented trellis GEMM of the reference, inner_mm_seg_mlx with its expert block
  * table, ponyexl3/mlx/gemv_metal.py:1519-1741 and ponyexl3/mlx/exl3_moe.py:79-99,685-768. */
 EXL3_API int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
                     const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
                     const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
                     const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
-                    int64_t y_row_stride, void* workspace, size_t workspace_bytes, unsigned flags,
-                    exl3_stream_t stream);
+                    int64_t y_row_stride, const int32_t* y_row_map, void* workspace, size_t workspace_bytes,
+                    unsigned flags, exl3_stream_t stream);
 
 /* exl3_gemv without a caller-supplied workspace, for callers that cannot allocate device
  * memory: operator slots of a serving framework or thin language bindings that are handed
@@ -273,6 +275,22 @@ EXL3_API int exl3_moe_decode_tables(const void* indices, int index_bytes, int n_
                                     int num_experts, int64_t d, int64_t h, int32_t* blocks_gu,
                                     int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* blocks_dn,
                                     int32_t* suh_row_dn, unsigned flags, exl3_stream_t stream);
+
+/* Prefill-class SwitchGLU tables, built on the device by one kernel (no host round trip): the
+ * n_pairs (token, slot) pairs are grouped by expert (a counting sort; the order inside an expert
+ * is not fixed, rows are independent), cut into row tiles of at most 256 pairs that never straddle
+ * two experts, and expanded into the tile tables exl3_gemm_tiles takes — the reference builds the
+ * same expert block table on the host, ponyexl3/mlx/exl3_moe.py:79-99,685-768.
+ *   order (n_pairs): sorted position -> pair (the y_row_map of the down launch);
+ *   row_src_gu, suh_row_gu (2*n_pairs): rotated rows [0,n) carry the gate signs, [n,2n) the up signs;
+ *   suh_row_dn (n_pairs); tiles_gu (2 * slots * ceil(h/256), 8): gate tiles then up tiles;
+ *   tiles_dn (slots * ceil(d/256), 8); slots = n_pairs / 256 + num_experts (unused ones are empty).
+ * n_pairs <= 2^20, num_experts <= 1024. */
+EXL3_API int exl3_moe_prefill_tables(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                     int num_experts, int64_t d, int64_t h, int32_t* order,
+                                     int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* suh_row_dn,
+                                     int32_t* tiles_gu, int32_t* tiles_dn, unsigned flags,
+                                     exl3_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -48,7 +48,7 @@ _PROTOTYPES = {
                           c_uint, c_void_p]),
     "exl3_gemm_tiles": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64,
-                                c_void_p, c_void_p, c_int64, c_void_p, c_size_t, c_uint, c_void_p]),
+                                c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_size_t, c_uint, c_void_p]),
     "exl3_gemv_noalloc": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int,
                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_uint,
                                   c_void_p]),
@@ -66,6 +66,8 @@ _PROTOTYPES = {
     "exl3_peer_allgather": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64,
                                     c_int64, c_uint, c_void_p]),
     "exl3_peer_wait": (c_int, [c_void_p, c_uint, c_void_p, c_uint, c_void_p]),
+    "exl3_moe_prefill_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
     "exl3_moe_decode_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
 }

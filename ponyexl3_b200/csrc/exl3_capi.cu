@@ -425,8 +425,8 @@ int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh
                     const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
                     const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
                     const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
-                    int64_t y_row_stride, void* workspace, size_t workspace_bytes, unsigned flags,
-                    exl3_stream_t stream)
+                    int64_t y_row_stride, const int32_t* y_row_map, void* workspace, size_t workspace_bytes,
+                    unsigned flags, exl3_stream_t stream)
 {
     (void)flags;
     if (!x || !trellis || !y || !tiles) return EXL3_E_NULL;
@@ -461,6 +461,7 @@ int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh
     a.status = reinterpret_cast<int*>(ws + kWsStatus);
     a.y_row_stride = y_row_stride;
     a.tile_tab = tiles;
+    a.y_row_map = y_row_map;
     a.n_tiles_tab = (int)n_tiles;
     a.xh_rows = (int)xh_rows;
     a.m = (int)xh_rows;

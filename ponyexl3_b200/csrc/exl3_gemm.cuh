@@ -288,7 +288,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     }
                     had128_regs(v);
                     if (row < ti.m_end) {
-                        __half* yp = a.y + (int64_t)(row + ti.y_row_delta) * a.y_row_stride + col0;
+                        const int orow = a.y_row_map ? a.y_row_map[row + ti.y_row_delta] : row + ti.y_row_delta;
+                        __half* yp = a.y + (int64_t)orow * a.y_row_stride + col0;
 #pragma unroll
                         for (int c = 0; c < 16; c++) {
                             float o[8];

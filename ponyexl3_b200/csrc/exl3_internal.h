@@ -112,6 +112,7 @@ struct GemmArgs {
     int* status;
     int64_t y_row_stride;
     const int32_t* tile_tab;  // grouped launches: device table of 8 ints per tile, else NULL
+    const int32_t* y_row_map; // grouped launches: output row of every computed row, or NULL (identity)
     int n_tiles_tab;          // slots in tile_tab
     int xh_rows;              // rows of the rotated-activation matrix
     int m;                    // rows (tokens)

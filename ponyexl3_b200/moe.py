@@ -149,6 +149,41 @@ class EXL3SwitchGLU(torch.nn.Module):
         return tab.reshape(-1, 8).to(torch.int32).contiguous()
 
     def _prefill(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        """Tables kernel, rotation + tile-table GEMM for gate and up, GLU, rotation + tile-table GEMM
+        for down writing straight back into (token, slot) order.  No host round trip."""
+        if self.activation != "silu":
+            return self._prefill_torch_tables(x2d, indices)
+        from . import _lib
+        E, D, H = self.num_experts, self.input_dims, self.hidden_dims
+        R, kk = indices.shape
+        n = R * kk
+        dev = x2d.device
+        idx = indices.reshape(-1)
+        if idx.dtype not in (torch.int32, torch.int64):
+            idx = idx.to(torch.int64)
+        idx = idx.contiguous()
+        slots = n // 256 + E
+        ct_h, ct_d = (H + 255) // 256, (D + 255) // 256
+        n_gu, n_dn = 2 * slots * ct_h * 8, slots * ct_d * 8
+        tab = torch.empty(n_gu + n_dn + 6 * n, dtype=torch.int32, device=dev)   # tiles first: 16-byte aligned
+        tiles_gu, tiles_dn = tab[:n_gu].view(-1, 8), tab[n_gu:n_gu + n_dn].view(-1, 8)
+        o = n_gu + n_dn
+        order, row_src = tab[o:o + n], tab[o + n:o + 3 * n]
+        suh_gu, suh_dn = tab[o + 3 * n:o + 5 * n], tab[o + 5 * n:o + 6 * n]
+        _lib.check(_lib.load().exl3_moe_prefill_tables(
+            idx.data_ptr(), idx.element_size(), n, kk, E, D, H, order.data_ptr(), row_src.data_ptr(),
+            suh_gu.data_ptr(), suh_dn.data_ptr(), tiles_gu.data_ptr(), tiles_dn.data_ptr(), 0,
+            torch.cuda.current_stream(dev).cuda_stream), "exl3_moe_prefill_tables")
+        ygu = torch.empty((n, 2 * H), dtype=torch.float16, device=dev)
+        ops.gemm_tiles(x2d, xh_rows=2 * n, row_src=row_src, suh=self._gu_suh, suh_row=suh_gu,
+                       trellis=self._gu_trellis, k=self.k, cb=self.cb, tiles=tiles_gu, svh=self._gu_svh, y=ygu)
+        h = ops.swiglu(ygu)
+        out = torch.empty((n, D), dtype=torch.float16, device=dev)
+        ops.gemm_tiles(h, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=suh_dn, trellis=self._dn_trellis,
+                       k=self.k, cb=self.cb, tiles=tiles_dn, svh=self._dn_svh, y=out, y_row_map=order)
+        return out.view(R, kk, D)
+
+    def _prefill_torch_tables(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
         E, D, H = self.num_experts, self.input_dims, self.hidden_dims
         R, kk = indices.shape
         n = R * kk

@@ -246,7 +246,8 @@ def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None
 
 def gemm_tiles(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None,
                suh: torch.Tensor | None, suh_row: torch.Tensor | None, trellis: torch.Tensor, k: int,
-               cb: int, tiles: torch.Tensor, svh: torch.Tensor | None, y: torch.Tensor) -> torch.Tensor:
+               cb: int, tiles: torch.Tensor, svh: torch.Tensor | None, y: torch.Tensor,
+               y_row_map: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core GEMM over a tile table (see exl3_gemm_tiles in the header).  `tiles` is an
     int32 CUDA tensor (n_tiles, 8); `y` (rows, cols) fp16 is written in place."""
     _need_cuda(x2d, "x")
@@ -264,7 +265,7 @@ def gemm_tiles(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None,
     _lib.check(lib.exl3_gemm_tiles(
         x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),
         ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), tiles.data_ptr(),
-        tiles.shape[0], ptr(svh), y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes, 0,
+        tiles.shape[0], ptr(svh), y.data_ptr(), y.stride(0), ptr(y_row_map), ws.buf.data_ptr(), ws.nbytes, 0,
         _stream(x2d.device)), "exl3_gemm_tiles")
     return y
 
