@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the EXL3 streamed GEMV (batch-1 decode) on B200.
 
-Workload (BASELINE.json configs[1], the one the metric is quoted on): the three
+Workload (the batch-1..16 GEMV sweep configuration the headline metric is quoted on): the three
 27B-class decode shapes 5120->17408 (gate/up), 17408->5120 (down) and 5120->5120
 (o_proj) at K = 4 bits/weight, 3INST codebook, one activation row, random packed
 trellis words and random +-1 sign vectors (seeded synthetic data; decode cost is
@@ -485,7 +485,7 @@ def run_gpu(args):
 
 
 def run_decode(args):
-    """BASELINE.json configs[4]: one greedy decode step of the synthetic 64-layer dense model
+    """The dense-transformer decode configuration: one greedy decode step of the synthetic 64-layer dense model
     (all linears EXL3, K in {4,5}, KV context 8192) at --rows new positions, tensor parallel by
     output tile over the launched ranks.  A step = one forward + arg-max, captured in a CUDA
     graph; value = rows / step time."""
@@ -633,7 +633,7 @@ def run_decode(args):
 
 
 def run_moe(args):
-    """BASELINE.json configs[3]: stacked-expert SwitchGLU, 256 experts, top-8, hidden 2048, expert
+    """The MoE expert-layer configuration: stacked-expert SwitchGLU, 256 experts, top-8, hidden 2048, expert
     intermediate 512, K=4, router logits N(0,1) -> softmax top-8, for --tokens 1, 16 or 4096.
     N > 1: experts partitioned by expert; few tokens are replicated and the partial outputs summed
     (all-reduce), many tokens are partitioned and their rows exchanged with two all-to-alls.
@@ -757,7 +757,7 @@ def run_moe(args):
 
 
 def run_sweep(args):
-    """BASELINE.json configs[1] in full: rows x K x codebook x shape, one graph-captured train
+    """The GEMV sweep configuration in full: rows x K x codebook x shape, one graph-captured train
     of launches over distinct layers (more packed bytes than L2) per case.  Prints one JSON
     line per case and, with --sweep-out, writes a markdown table."""
     import torch

@@ -102,46 +102,62 @@ __global__ void __launch_bounds__(256)
     const int64_t total = rows * nblk;
     const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
-    for (int64_t i = warp0; i < total; i += nwarps) {
-        const int64_t r = i / nblk, b = i % nblk;
-        const int64_t col = b * 128 + lane * 4;
-        const int64_t rs = row_src ? row_src[r] : r;
-        float v[4];
-        load4<T>(x + rs * x_row_stride + col, v);
-        // the reference rounds x to fp16 first (ponyexl3/ref/forward.py:26)
+    // Four 128-blocks per warp and turn: the loads of all four are in flight before the first
+    // butterfly starts (one 256-byte load per warp at a time left the kernel latency-bound).
+    constexpr int U = 4;
+    for (int64_t i0 = warp0; i0 < total; i0 += nwarps * U) {
+        float v[U][4], sp[U][4];
+        int64_t rr[U], cc[U];
 #pragma unroll
-        for (int q = 0; q < 4; q++) v[q] = __half2float(__float2half_rn(v[q]));
-        if (pre) {
-            float s[4];
-            load4<__half>(pre + (pre_row ? (int64_t)pre_row[r] * n : 0) + col, s);
-#pragma unroll
-            for (int q = 0; q < 4; q++) v[q] *= s[q];
+        for (int u = 0; u < U; u++) {
+            const int64_t i = i0 + u * nwarps;       // strided: small problems still use every warp
+            const bool ok = i < total;
+            const int64_t r = ok ? i / nblk : 0, b = ok ? i % nblk : 0;
+            rr[u] = ok ? r : -1;
+            cc[u] = b * 128 + lane * 4;
+            const int64_t rs = row_src ? row_src[r] : r;
+            load4<T>(x + rs * x_row_stride + cc[u], v[u]);
+            if (pre) load4<__half>(pre + (pre_row ? (int64_t)pre_row[r] * n : 0) + cc[u], sp[u]);
         }
-        had128_warp(v, lane);
 #pragma unroll
-        for (int q = 0; q < 4; q++) v[q] *= EXL3_HAD_SCALE;
-        if (post) {
-            float s[4];
-            load4<__half>(post + (post_row ? (int64_t)post_row[r] * n : 0) + col, s);
+        for (int u = 0; u < U; u++) {
+            // the reference rounds x to fp16 first (ponyexl3/ref/forward.py:26)
 #pragma unroll
-            for (int q = 0; q < 4; q++) v[q] *= s[q];
+            for (int q = 0; q < 4; q++) {
+                v[u][q] = __half2float(__float2half_rn(v[u][q]));
+                if (pre) v[u][q] *= sp[u][q];
+            }
+            had128_warp(v[u], lane);
         }
-        uint2 o;
-        o.x = h2_as_u32(__floats2half2_rn(v[0], v[1]));
-        o.y = h2_as_u32(__floats2half2_rn(v[2], v[3]));
-        if (out_mode == HAD_OUT_F16) {
-            *reinterpret_cast<uint2*>(out + r * n + col) = o;
-        } else {
-            // one 32-bit word per element for the GEMV's two-slot fragments:
-            // (x, 0) keeps exactly-decoded weights, (x, x) lets the MMA add the two
-            // codebook halves itself
-            uint4 e;
-            const uint32_t m = (out_mode == HAD_OUT_PAIR_X0) ? 0u : 0x00010000u;
-            e.x = (o.x & 0xFFFFu) * (1u + m);
-            e.y = (o.x >> 16) * (1u + m);
-            e.z = (o.y & 0xFFFFu) * (1u + m);
-            e.w = (o.y >> 16) * (1u + m);
-            *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + r * n + col) = e;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (rr[u] < 0) continue;
+            const int64_t r = rr[u], col = cc[u];
+#pragma unroll
+            for (int q = 0; q < 4; q++) v[u][q] *= EXL3_HAD_SCALE;
+            if (post) {
+                float s[4];
+                load4<__half>(post + (post_row ? (int64_t)post_row[r] * n : 0) + col, s);
+#pragma unroll
+                for (int q = 0; q < 4; q++) v[u][q] *= s[q];
+            }
+            uint2 o;
+            o.x = h2_as_u32(__floats2half2_rn(v[u][0], v[u][1]));
+            o.y = h2_as_u32(__floats2half2_rn(v[u][2], v[u][3]));
+            if (out_mode == HAD_OUT_F16) {
+                *reinterpret_cast<uint2*>(out + r * n + col) = o;
+            } else {
+                // one 32-bit word per element for the GEMV's two-slot fragments:
+                // (x, 0) keeps exactly-decoded weights, (x, x) lets the MMA add the two
+                // codebook halves itself
+                uint4 e;
+                const uint32_t m = (out_mode == HAD_OUT_PAIR_X0) ? 0u : 0x00010000u;
+                e.x = (o.x & 0xFFFFu) * (1u + m);
+                e.y = (o.x >> 16) * (1u + m);
+                e.z = (o.y & 0xFFFFu) * (1u + m);
+                e.w = (o.y >> 16) * (1u + m);
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + r * n + col) = e;
+            }
         }
     }
 }
