@@ -239,9 +239,9 @@ EXL3_API int exl3_swiglu(const uint16_t* gate_up, int64_t gu_row_stride, uint16_
  * GPU) and passes the W device pointers as HOST arrays.
  *
  * exl3_gemv_peers: exl3_gemv whose epilogue stores each finished 128-column block at column
- *   col0 + block * 128 of EVERY rank's (rows, full_row_stride) buffer and then adds 1 to every
- *   rank's counter.  A rank's full row is complete when its counter has grown by the number of
- *   blocks of the whole layer (out_features_total / 128).
+ *   col0 + block * 128 of EVERY rank's (rows, full_row_stride) buffer; the CTA that finishes the
+ *   rank's last block then adds 1 to every rank's counter (one system-scope release per launch).
+ *   A rank's full row is complete when its counter has grown by n_peers.
  * exl3_peer_allgather: the same exchange for a (rows, cols) slice computed by other kernels;
  *   one arrival per rank, so the full row is complete after n_peers arrivals.
  * exl3_peer_wait: one-thread kernel that polls this rank's counter until `target` arrivals are

@@ -276,6 +276,7 @@ static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_strid
 #endif
     a.n_peer = peer.n;
     a.y_col0 = peer.col0;
+    a.done_ctr = reinterpret_cast<unsigned*>(ws + kWsDoneCtr);
     for (int p = 0; p < peer.n; p++) {
         a.y_peer[p] = reinterpret_cast<__half*>(peer.y[p]);
         a.ctr_peer[p] = reinterpret_cast<unsigned*>(peer.ctr[p]);

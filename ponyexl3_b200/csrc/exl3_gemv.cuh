@@ -555,13 +555,23 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
                 // all-gather fused into the epilogue: the block lands in every rank's full row
                 const int64_t off = (int64_t)n * a.y_row_stride + a.y_col0 + y_off + 4 * lane;
                 for (int p = 0; p < a.n_peer; p++) *reinterpret_cast<uint2*>(a.y_peer[p] + off) = ov;
-                __threadfence_system();
             }
         }
         if (a.n_peer > 0) {
+            // System-scope fences are expensive and queue up behind one another, so only ONE thread of
+            // the whole grid pays for them: every block is counted on a local counter (GPU scope),
+            // and the CTA that finishes the last block of this rank announces the rank to all peers.
             named_bar_sync(1, kConsumerThreads);          // every row of the block has been sent
-            if (tid < a.n_peer)
-                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.ctr_peer[tid]) : "memory");
+            if (tid == 0) {
+                __threadfence();
+                const unsigned done = atomicAdd(a.done_ctr, 1u) + 1u;
+                if (done == (unsigned)a.ncb) {
+                    atomicExch(a.done_ctr, 0u);           // re-armed for the next launch on this workspace
+                    __threadfence_system();
+                    for (int p = 0; p < a.n_peer; p++)
+                        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.ctr_peer[p]) : "memory");
+                }
+            }
         }
         if (cbi + 1 < n_cb) {
             // more blocks follow: tell the others that the landing slots are free again

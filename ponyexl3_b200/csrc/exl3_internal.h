@@ -37,6 +37,7 @@ inline int launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t s
 // [256, ...)    scratch: the rotated activations xh of the current call — one 32-bit word per
 //               element for the GEMV when the rotation is not fused, fp16 for the GEMM
 constexpr size_t kWsStatus = 0;
+constexpr size_t kWsDoneCtr = 64;   // finished-block counter of a launch with peer outputs (inside the status area)
 constexpr size_t kWsScratch = 256;
 
 // ---- launchers -------------------------------------------------------------------------------
@@ -97,7 +98,8 @@ struct GemvArgs {
     int n_peer;
     int64_t y_col0;            // this rank's first column inside the full row
     __half* y_peer[8];         // full-width (rows, y_row_stride) buffers of all ranks, this one included
-    unsigned* ctr_peer[8];     // arrival counters of all ranks (one increment per finished block)
+    unsigned* ctr_peer[8];     // arrival counters of all ranks (one increment per rank and launch)
+    unsigned* done_ctr;        // local: finished blocks of this launch (the last one announces the rank)
 };
 constexpr int kMaxPeers = 8;
 

@@ -372,7 +372,7 @@ def gemv_peers(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh, s
         x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out, k, int(cb),
         ptr(suh), ptr(svh), ptr(bias), y_ptrs, c_ptrs, exchange.world, out_features_total, int(col0),
         ws.buf.data_ptr(), ws.nbytes, _lib.FLAG_PDL if pdl else 0, _stream(x2d.device)), "exl3_gemv_peers")
-    _lib.check(lib.exl3_peer_wait(my_ctr, out_features_total // 128, ws.buf.data_ptr(), _flags(pdl),
+    _lib.check(lib.exl3_peer_wait(my_ctr, exchange.world, ws.buf.data_ptr(), _flags(pdl),
                                   _stream(x2d.device)), "exl3_peer_wait")
     return view
 

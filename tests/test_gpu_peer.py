@@ -53,7 +53,7 @@ def test_gemv_peers_single_peer_equals_gemv(lib, rows, k):
                              suh.data_ptr(), svh.data_ptr(), None, _u64(y_full.data_ptr()), _u64(ctr.data_ptr()),
                              1, full, col0, ws.data_ptr(), n, 0, st)
     assert rc == 0
-    assert lib.exl3_peer_wait(ctr.data_ptr(), outf // 128, ws.data_ptr(), 0, st) == 0
+    assert lib.exl3_peer_wait(ctr.data_ptr(), 1, ws.data_ptr(), 0, st) == 0
     torch.cuda.synchronize()
     assert _status(lib, ws) == 0
     assert int(ctr[0]) == 0                                     # re-armed by the waiter
