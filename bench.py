@@ -702,7 +702,9 @@ def run_moe(args):
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
-        if (T <= 16 or world == 1) and not args.no_graph:      # no host round trip in these paths
+        # one GPU: no host round trip anywhere, the call is captured.  Expert parallel: each rank
+        # picks its pairs with a host-visible count (nonzero / split sizes), so it runs eagerly.
+        if world == 1 and not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()
