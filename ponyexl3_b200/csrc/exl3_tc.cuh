@@ -1,6 +1,6 @@
 // Thin wrappers over the sm_100a tensor-core instructions used by the prefill GEMM:
 // tensor-memory allocation, tcgen05.mma with shared-memory descriptors, commit to an
-// mbarrier, and tensor-memory loads for the epilogue.  cta_group::1 only, no multicast.
+// mbarrier, and tensor-memory loads for the epilogue.  cta_group::1 only: one CTA per tile.
 #pragma once
 #include <stdint.h>
 

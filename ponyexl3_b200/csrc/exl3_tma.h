@@ -1,6 +1,6 @@
 // Host-side construction of TMA tensor maps (cuTensorMapEncodeTiled, reached through
 // cudaGetDriverEntryPoint so the library links against the runtime only) and the device
-// wrappers of the tiled tensor copies.  None of the copies uses cluster multicast.
+// wrappers of the tiled tensor copies.  Every copy lands in the issuing CTA's own shared memory.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
