@@ -349,10 +349,15 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
     const bool pdl = (flags & EXL3_FLAG_PDL) != 0;
     const bool fast = (flags & EXL3_FLAG_FAST_ACCUM) != 0 && cb != CB_MUL1;
     cudaStream_t s = (cudaStream_t)stream;
-    rc = launch_hadamard(x, x_dtype, xh_rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
-                         nullptr, reinterpret_cast<__half*>(xh), row_src, suh_row, nullptr, pdl,
-                         fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s);
-    if (rc) return rc;
+    // One block per cluster and few rows: the kernel rotates its own row; else a rotation kernel
+    // fills the workspace first.
+    const bool x_fused = gemv_blocks_x_is_fused(rows, (int)t_in, (int)n_blocks);
+    if (!x_fused) {
+        rc = launch_hadamard(x, x_dtype, xh_rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
+                             nullptr, reinterpret_cast<__half*>(xh), row_src, suh_row, nullptr, pdl,
+                             fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s);
+        if (rc) return rc;
+    }
     GemvArgs a = {};
     a.trellis = reinterpret_cast<const uint32_t*>(trellis);
     a.xh = xh;
@@ -369,7 +374,13 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
     a.x_rows_total = (int)xh_rows;
     a.raw_out = raw_out ? 1 : 0;
     a.fast_accum = fast ? 1 : 0;
-    a.x_fused = 0;
+    a.x = x;
+    a.suh = reinterpret_cast<const __half*>(suh);
+    a.x_row_stride = x_row_stride;
+    a.x_dtype = x_dtype;
+    a.x_fused = x_fused ? 1 : 0;
+    a.row_src = row_src;
+    a.suh_row = suh_row;
     return launch_gemv(a, k, cb, pdl, s);
 }
 

@@ -81,6 +81,16 @@ bool gemv_x_is_fused(int rows, int t_in, int ncb)
     return (klen * rows + 1) * kXsRowBytesHost <= g_fuse_x_bytes;
 }
 
+// A block-table launch can rotate its activations in the kernel when every cluster computes a
+// single block: the CTA then needs one (rotated row, sign vector) pair for its whole life.
+bool gemv_blocks_x_is_fused(int rows, int t_in, int ncb)
+{
+    if (!gemv_x_is_fused(rows, t_in, ncb)) return false;
+    int s, grid;
+    gemv_choose_split(ncb, t_in >> 3, rows, &s, &grid);
+    return ncb <= grid / s;
+}
+
 template <int K> int launch_gemv_k(const GemvArgs& a, int cb, bool pdl, cudaStream_t s);
 extern template int launch_gemv_k<1>(const GemvArgs&, int, bool, cudaStream_t);
 extern template int launch_gemv_k<2>(const GemvArgs&, int, bool, cudaStream_t);

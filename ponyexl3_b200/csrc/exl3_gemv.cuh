@@ -302,18 +302,28 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         const int rows = a.rows;
         const int ntask = rows * klen;               // one (row, k-block) per warp and turn
         const int zero_off = klen * rows * kXsRowBytes;
+        // Block-table launches (one block per cluster here): rotated row xrow0 + r of the table's
+        // numbering is x[row_src[..]] with the sign vector suh[suh_row[..]]; the table belongs to an
+        // earlier kernel of the stream, so nothing of it is read before the dependency wait.
+        int xrow0 = 0;
         auto task_col = [&](int task) {
             const int r = task / klen;
             return (int64_t)(kb0 + task - r * klen) * 128 + lane * 4;
         };
         auto load_scale = [&](int task, float (&sc)[4]) {
-            if (a.suh && task < ntask) load4_any<__half>(a.suh + task_col(task), sc);
-            else sc[0] = sc[1] = sc[2] = sc[3] = 1.f;
+            if (a.suh && task < ntask) {
+                const int r = task / klen;
+                const int64_t srow = a.suh_row ? a.suh_row[xrow0 + r] : 0;
+                load4_any<__half>(a.suh + srow * ((int64_t)a.t_in * 16) + task_col(task), sc);
+            } else {
+                sc[0] = sc[1] = sc[2] = sc[3] = 1.f;
+            }
         };
         auto load_x = [&](int task, float (&v)[4]) {
             if (task >= ntask) return;
-            const int r = task / klen;
-            const int64_t off = (int64_t)r * a.x_row_stride + task_col(task);
+            const int r0 = task / klen;
+            const int64_t r = a.row_src ? a.row_src[xrow0 + r0] : xrow0 + r0;
+            const int64_t off = r * a.x_row_stride + task_col(task);
             if (a.x_dtype == EXL3_DT_F16) load4_any<__half>(reinterpret_cast<const __half*>(a.x) + off, v);
             else if (a.x_dtype == EXL3_DT_BF16)
                 load4_any<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(a.x) + off, v);
@@ -336,14 +346,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
         // suh is a weight: the first two turns' scales are fetched while the previous kernel
         // of the stream may still be running; x belongs to it until the dependency wait.
         float sc0[4], sc1[4], v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
-        load_scale(warp, sc0);
-        load_scale(warp + kConsumerWarps, sc1);
+        if (!a.blocks) {
+            load_scale(warp, sc0);
+            load_scale(warp + kConsumerWarps, sc1);
+        }
         griddep_wait();
 #ifdef EXL3_PROFILE
         gt_dep = global_ns();
 #endif
+        if (a.blocks) xrow0 = a.blocks[cluster_id < a.ncb ? cluster_id : 0].xrow;
         for (int task = warp; task < ntask; task += 2 * kConsumerWarps) {
-            if (task != warp) {
+            if (task != warp || a.blocks) {
                 load_scale(task, sc0);
                 load_scale(task + kConsumerWarps, sc1);
             }

@@ -86,6 +86,8 @@ struct GemvArgs {
     int64_t x_row_stride;
     int x_dtype;
     int x_fused;               // 1: rotate x in the kernel; 0: xh was written by the rotation kernel
+    const int32_t* row_src;    // fused rotation of a block-table launch: x row of rotated row i (NULL: i)
+    const int32_t* suh_row;    // ... and its row of the stacked suh matrix (NULL: row 0)
     // filled in by the launcher
     long long* prof;           // EXL3_PROFILE builds: per-warp cycle counters; NULL otherwise
     uint32_t sixteen;          // the number 16 as a run-time value (keeps shifts on the multiplier)
@@ -105,6 +107,7 @@ constexpr int kMaxPeers = 8;
 
 int launch_gemv(const GemvArgs& a, int k, int cb, bool pdl, cudaStream_t s);
 bool gemv_x_is_fused(int rows, int t_in, int ncb);
+bool gemv_blocks_x_is_fused(int rows, int t_in, int ncb);   // block tables: only with one block per cluster
 
 // ---- prefill GEMM (exl3_gemm.cuh) ---------------------------------------------------------
 struct GemmArgs {
