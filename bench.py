@@ -621,9 +621,11 @@ def run_decode(args):
             "e2e": {"value": rows / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8 * rows,
                     "d2h_bytes_per_step": 8 * rows, "ms_per_step": 1e3 * e2e_s,
                     "api": "SyntheticDenseDecoder.step, token ids from and to pinned host memory"},
-            # per layer: 2 norms, 2 rotations, 4 GEMVs, rotary, 2 attention, SwiGLU (+ 2 copies and 4
-            # waits with the peer exchange); then the final norm and the head
-            "gpu_launches": (cfg.layers * (12 + (6 if dec.peer is not None else 0)) + 2) * args.steps,
+            # per layer: 2 norms, 4 GEMVs (rotations inside for up to 8 rows, else 4 rotation kernels),
+            # rotary, 2 attention, SwiGLU (+ 2 copies and 4 waits with the peer exchange); then the
+            # final norm and the head
+            "gpu_launches": (cfg.layers * (10 + (4 if rows > 8 else 0) + (6 if dec.peer is not None else 0)) + 2
+                             + (1 if rows > 8 else 0)) * args.steps,
             "clocks": clocks, "kernel_status": status,
         }
         emit(line)
