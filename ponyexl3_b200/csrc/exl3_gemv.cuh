@@ -580,9 +580,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2)
                 const unsigned done = atomicAdd(a.done_ctr, 1u) + 1u;
                 if (done == (unsigned)a.ncb) {
                     atomicExch(a.done_ctr, 0u);           // re-armed for the next launch on this workspace
-                    __threadfence_system();
+                    __threadfence_system();               // one fence orders all blocks before all arrivals
                     for (int p = 0; p < a.n_peer; p++)
-                        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.ctr_peer[p]) : "memory");
+                        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(a.ctr_peer[p]) : "memory");
                 }
             }
         }

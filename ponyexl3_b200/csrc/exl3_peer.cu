@@ -60,8 +60,11 @@ __global__ void __launch_bounds__(512) peer_allgather_kernel(const PeerCopyArgs 
     }
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x < a.n_peer)
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.ctr[threadIdx.x]) : "memory");
+    if (threadIdx.x == 0) {
+        __threadfence_system();                   // the CTA's stores (ordered by the barrier), then the arrivals
+        for (int p = 0; p < a.n_peer; p++)
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(a.ctr[p]) : "memory");
+    }
 }
 
 }  // namespace exl3
