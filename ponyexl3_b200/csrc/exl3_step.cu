@@ -160,6 +160,7 @@ struct AttnArgs {
     __half* out;              // (rows, hq * 128)
     int64_t cache_len;
     int rows, hq, hkv, group, ctx, chunk, nsplit;
+    int nbuf;                 // shared-memory tile buffers per tensor: 2 (double buffer) or 1 (one-tile chunks)
     float scale_log2;         // log2(e) / sqrt(128)
 };
 
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(NW * 32) attn_partial_kernel(const AttnArgs a)
     const int ntiles = (p1 - p0 + kAttnTile - 1) / kAttnTile;
     const __half* kbase = a.k_cache + (int64_t)kvh * a.cache_len * 128;
     const __half* vbase = a.v_cache + (int64_t)kvh * a.cache_len * 128;
-    const uint32_t s_k = smem_u32(smem), s_v = s_k + 2 * kAttnTileBytes;   // [2] K tiles, then [2] V tiles
+    const uint32_t s_k = smem_u32(smem), s_v = s_k + a.nbuf * kAttnTileBytes;   // K tile buffers, then V tile buffers
 
     auto load_tile = [&](int ti, int buf) {
         const int key0 = p0 + ti * kAttnTile;
@@ -221,7 +222,7 @@ __global__ void __launch_bounds__(NW * 32) attn_partial_kernel(const AttnArgs a)
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
 
     for (int ti = 0; ti < ntiles; ti++) {
-        const int buf = ti & 1;
+        const int buf = ti & (a.nbuf - 1);
         if (ti + 1 < ntiles) {
             load_tile(ti + 1, buf ^ 1);
             cp_async_wait<1>();
@@ -325,24 +326,27 @@ __global__ void __launch_bounds__(NW * 32) attn_partial_kernel(const AttnArgs a)
 }
 
 // out[r, head, :] = sum_i 2^(m_i - m*) O_i / sum_i 2^(m_i - m*) l_i over the chunks i.
-// 128 features x 4 chunk lanes per CTA: lane j takes chunks j, j + 4, ... so the loads of the
-// (up to a few dozen) chunks are in flight together instead of one after the other.
-__global__ void __launch_bounds__(512) attn_combine_kernel(const AttnArgs a)
+// 128 features x 8 chunk lanes per CTA: lane j takes chunks j, j + 8, ... so the loads of the
+// (dozens to a hundred and more) chunks are in flight together instead of one after the other.
+constexpr int kCombineLanes = 8;
+__global__ void __launch_bounds__(128 * kCombineLanes) attn_combine_kernel(const AttnArgs a)
 {
     griddep_launch_dependents();
     griddep_wait();
-    __shared__ float s_acc[4][128], s_l[4], s_m[4];
+    __shared__ float s_acc[kCombineLanes][128], s_l[kCombineLanes], s_m[kCombineLanes];
     const int m = blockIdx.x, kvh = blockIdx.y, d = threadIdx.x & 127, j = threadIdx.x >> 7;
     const int M = a.group * a.rows;
     const int64_t base = (int64_t)kvh * a.nsplit * M + m;
     float mloc = -INFINITY;
-    for (int i = j; i < a.nsplit; i += 4) mloc = fmaxf(mloc, a.part_ml[(base + (int64_t)i * M) * 2]);
+    for (int i = j; i < a.nsplit; i += kCombineLanes) mloc = fmaxf(mloc, a.part_ml[(base + (int64_t)i * M) * 2]);
     if (d == 0) s_m[j] = mloc;
     __syncthreads();
-    const float mmax = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    float mmax = s_m[0];
+#pragma unroll
+    for (int q = 1; q < kCombineLanes; q++) mmax = fmaxf(mmax, s_m[q]);
     float acc = 0.f, lsum = 0.f;
 #pragma unroll 4
-    for (int i = j; i < a.nsplit; i += 4) {
+    for (int i = j; i < a.nsplit; i += kCombineLanes) {
         const int64_t row = base + (int64_t)i * M;
         const float mi = a.part_ml[row * 2];
         const float w = mi == -INFINITY ? 0.f : exp2f(mi - mmax);   // a chunk this row does not see
@@ -353,8 +357,12 @@ __global__ void __launch_bounds__(512) attn_combine_kernel(const AttnArgs a)
     if (d == 0) s_l[j] = lsum;
     __syncthreads();
     if (j == 0) {
-        const float num = s_acc[0][d] + s_acc[1][d] + s_acc[2][d] + s_acc[3][d];
-        const float den = s_l[0] + s_l[1] + s_l[2] + s_l[3];
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int q = 0; q < kCombineLanes; q++) {
+            num += s_acc[q][d];
+            den += s_l[q];
+        }
         const int gq = m / a.rows, r = m - gq * a.rows;
         a.out[((int64_t)r * a.hq + kvh * a.group + gq) * 128 + d] = __float2half_rn(num / den);
     }
@@ -362,13 +370,13 @@ __global__ void __launch_bounds__(512) attn_combine_kernel(const AttnArgs a)
 
 template <int NW> static int launch_attn_partial(const AttnArgs& a, cudaStream_t s, bool pdl)
 {
-    const size_t smem = 4 * (size_t)kAttnTileBytes;
+    const size_t smem = 2 * (size_t)a.nbuf * kAttnTileBytes;
     static bool set[16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 16 && !set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+                                             4 * kAttnTileBytes);
         if (e != cudaSuccess) return note_cuda(e);
         set[dev] = true;
     }
@@ -376,15 +384,18 @@ template <int NW> static int launch_attn_partial(const AttnArgs& a, cudaStream_t
                          pdl, a);
 }
 
-// Chunking: about two CTAs per SM, chunks a multiple of the 64-key tile.
-static void attn_plan(int total_keys, int hkv, int m_rows, int* chunk, int* nsplit)
+// Chunking.  A CTA has one warp per 16 query rows, so with few query rows (decode: group x 1) the
+// work of a chunk is one warp's: chunks are then a single 64-key tile and there are many of them
+// (about eight small CTAs per SM); with more rows, about two CTAs per SM and double-buffered tiles.
+static void attn_plan(int total_keys, int hkv, int m_rows, int* chunk, int* nsplit, int* nbuf)
 {
-    int want = std::max(1, 2 * device_sm_count() / std::max(1, hkv));
-    if (m_rows > 64) want = std::max(1, want / 2);      // partial outputs grow with M
+    const int per_sm = m_rows <= 16 ? 8 : (m_rows <= 64 ? 2 : 1);
+    const int want = std::max(1, per_sm * device_sm_count() / std::max(1, hkv));
     int c = (total_keys + want - 1) / want;
     c = (c + kAttnTile - 1) / kAttnTile * kAttnTile;
     *chunk = c;
     *nsplit = (total_keys + c - 1) / c;
+    *nbuf = c > kAttnTile ? 2 : 1;
 }
 
 }  // namespace exl3
@@ -435,9 +446,9 @@ extern "C" int exl3_swiglu(const uint16_t* gate_up, int64_t gu_row_stride, uint1
 extern "C" size_t exl3_attn_workspace_bytes(int rows, int q_heads, int kv_heads, int64_t total_keys)
 {
     if (rows < 1 || q_heads < 1 || kv_heads < 1 || q_heads % kv_heads || total_keys < 1) return 0;
-    int chunk, nsplit;
+    int chunk, nsplit, nbuf;
     const int m = q_heads / kv_heads * rows;
-    attn_plan((int)total_keys, kv_heads, m, &chunk, &nsplit);
+    attn_plan((int)total_keys, kv_heads, m, &chunk, &nsplit, &nbuf);
     return (size_t)kv_heads * nsplit * m * (128 + 2) * sizeof(float) + 256;
 }
 
@@ -460,7 +471,7 @@ extern "C" int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, cons
     a.out = reinterpret_cast<__half*>(out);
     a.cache_len = cache_len;
     a.rows = rows; a.hq = q_heads; a.hkv = kv_heads; a.group = group; a.ctx = ctx;
-    attn_plan(ctx + rows, kv_heads, m, &a.chunk, &a.nsplit);
+    attn_plan(ctx + rows, kv_heads, m, &a.chunk, &a.nsplit, &a.nbuf);
     const size_t need = (size_t)kv_heads * a.nsplit * m * (128 + 2) * sizeof(float);
     if (workspace_bytes < need) return EXL3_E_WORKSPACE;
     a.part_o = static_cast<float*>(workspace);
@@ -480,5 +491,6 @@ extern "C" int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, cons
         default: rc = launch_attn_partial<8>(a, s, pdl); break;
     }
     if (rc) return rc;
-    return launch_kernel(attn_combine_kernel, dim3((unsigned)m, (unsigned)kv_heads), dim3(512), 0, s, pdl, a);
+    return launch_kernel(attn_combine_kernel, dim3((unsigned)m, (unsigned)kv_heads), dim3(128 * kCombineLanes), 0, s,
+                         pdl, a);
 }
