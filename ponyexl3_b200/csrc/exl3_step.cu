@@ -384,13 +384,14 @@ template <int NW> static int launch_attn_partial(const AttnArgs& a, cudaStream_t
                          pdl, a);
 }
 
-// Chunking.  A CTA has one warp per 16 query rows, so with few query rows (decode: group x 1) the
-// work of a chunk is one warp's: chunks are then a single 64-key tile and there are many of them
-// (about eight small CTAs per SM); with more rows, about two CTAs per SM and double-buffered tiles.
+// Chunking: about two CTAs per SM (a CTA of the verify shape, 5 warps at 170 registers, fits twice),
+// chunks a multiple of the 64-key tile.  One CTA per SM was tried for many query rows and left the
+// kernel bound by the latency of a single CTA's MMA chain (41 us at 16 rows); single-tile chunks
+// were tried for one row and only moved time into the combine kernel.
 static void attn_plan(int total_keys, int hkv, int m_rows, int* chunk, int* nsplit, int* nbuf)
 {
-    const int per_sm = m_rows <= 16 ? 8 : (m_rows <= 64 ? 2 : 1);
-    const int want = std::max(1, per_sm * device_sm_count() / std::max(1, hkv));
+    (void)m_rows;
+    const int want = std::max(1, 2 * device_sm_count() / std::max(1, hkv));
     int c = (total_keys + want - 1) / want;
     c = (c + kAttnTile - 1) / kAttnTile * kAttnTile;
     *chunk = c;
