@@ -224,13 +224,18 @@ class PeerExchange:
     def ring_for(exchanges_per_replay: int) -> int:
         """Smallest ring >= 3 whose rotation never puts the last exchange of a replayed sequence and
         the first of the next replay on the same pair."""
+        if exchanges_per_replay < 2:
+            raise ValueError("a replayed sequence needs at least two exchanges: with one, every replay "
+                             "would land on the same pair back to back")
         r = 3
-        while (exchanges_per_replay - 1) % r == 0 and exchanges_per_replay > 1:
+        while (exchanges_per_replay - 1) % r == 0:
             r += 1
         return r
 
     def restart(self) -> None:
-        """Start the rotation over (call at the top of every step, eager or captured)."""
+        """Start the rotation over: call at the top of a sequence that is captured in a CUDA graph
+        and replayed, so that every replay (and the eager run before the capture) walks the same
+        pairs.  Purely eager callers need not restart at all."""
         self._next = 0
 
     def take(self, rows: int, cols: int):

@@ -60,6 +60,20 @@ def test_shard_ranges_cover_everything_once():
         shard_blocks(8, 2, 2)
 
 
+def test_peer_exchange_ring_never_reuses_a_pair_back_to_back():
+    """A replayed sequence of G exchanges over a ring of R pairs uses pair j % R; the last exchange
+    of one replay and the first of the next must differ, like any two neighbours."""
+    from ponyexl3_b200.parallel import PeerExchange
+
+    for g in list(range(2, 40)) + [48, 256, 257, 258]:
+        r = PeerExchange.ring_for(g)
+        assert r >= 3
+        seq = [j % r for j in range(g)] * 3                  # three replays back to back
+        assert all(a != b for a, b in zip(seq, seq[1:])), (g, r)
+    with pytest.raises(ValueError):
+        PeerExchange.ring_for(1)
+
+
 def _tp_worker(rank, world, outf):
     from conftest import synthetic_layer
     from oracle import exl3_oracle as oracle
