@@ -326,45 +326,57 @@ __global__ void __launch_bounds__(NW * 32) attn_partial_kernel(const AttnArgs a)
 }
 
 // out[r, head, :] = sum_i 2^(m_i - m*) O_i / sum_i 2^(m_i - m*) l_i over the chunks i.
-// 128 features x 8 chunk lanes per CTA: lane j takes chunks j, j + 8, ... so the loads of the
-// (dozens to a hundred and more) chunks are in flight together instead of one after the other.
-constexpr int kCombineLanes = 8;
-__global__ void __launch_bounds__(128 * kCombineLanes) attn_combine_kernel(const AttnArgs a)
+// One CTA per query row: L chunk lanes (about a quarter of the chunk count, 4..32) x 32 threads of
+// four features.  Lane j folds chunks j, j + L, ... into a running (max, sum, output) in ONE pass — the loads of a lane do not depend on
+// its running state, so they are all in flight together — and the lanes are merged through shared
+// memory by the same rule.  (A two-pass version with a thread per feature took as long as the
+// partial kernel at 16 rows.)
+constexpr int kCombineMaxLanes = 32;
+__global__ void __launch_bounds__(32 * kCombineMaxLanes) attn_combine_kernel(const AttnArgs a)
 {
     griddep_launch_dependents();
     griddep_wait();
-    __shared__ float s_acc[kCombineLanes][128], s_l[kCombineLanes], s_m[kCombineLanes];
-    const int m = blockIdx.x, kvh = blockIdx.y, d = threadIdx.x & 127, j = threadIdx.x >> 7;
+    __shared__ float4 s_acc[kCombineMaxLanes][32];
+    __shared__ float s_l[kCombineMaxLanes], s_m[kCombineMaxLanes];
+    const int m = blockIdx.x, kvh = blockIdx.y, d4 = threadIdx.x & 31, j = threadIdx.x >> 5;
+    const int lanes = blockDim.x >> 5;
     const int M = a.group * a.rows;
     const int64_t base = (int64_t)kvh * a.nsplit * M + m;
-    float mloc = -INFINITY;
-    for (int i = j; i < a.nsplit; i += kCombineLanes) mloc = fmaxf(mloc, a.part_ml[(base + (int64_t)i * M) * 2]);
-    if (d == 0) s_m[j] = mloc;
-    __syncthreads();
-    float mmax = s_m[0];
-#pragma unroll
-    for (int q = 1; q < kCombineLanes; q++) mmax = fmaxf(mmax, s_m[q]);
-    float acc = 0.f, lsum = 0.f;
+    float mrun = -INFINITY, lrun = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-    for (int i = j; i < a.nsplit; i += kCombineLanes) {
+    for (int i = j; i < a.nsplit; i += lanes) {
         const int64_t row = base + (int64_t)i * M;
-        const float mi = a.part_ml[row * 2];
-        const float w = mi == -INFINITY ? 0.f : exp2f(mi - mmax);   // a chunk this row does not see
-        acc += w * a.part_o[row * 128 + d];
-        lsum += w * a.part_ml[row * 2 + 1];
+        const float2 ml = *reinterpret_cast<const float2*>(a.part_ml + row * 2);
+        const float4 o = *reinterpret_cast<const float4*>(a.part_o + row * 128 + 4 * d4);
+        if (ml.x == -INFINITY) continue;                    // a chunk this row does not see at all
+        const float mnew = fmaxf(mrun, ml.x);
+        const float so = exp2f(mrun - mnew), sn = exp2f(ml.x - mnew);   // so = 0 on the first chunk
+        acc.x = acc.x * so + o.x * sn; acc.y = acc.y * so + o.y * sn;
+        acc.z = acc.z * so + o.z * sn; acc.w = acc.w * so + o.w * sn;
+        lrun = lrun * so + ml.y * sn;
+        mrun = mnew;
     }
-    s_acc[j][d] = acc;
-    if (d == 0) s_l[j] = lsum;
+    s_acc[j][d4] = acc;
+    if (d4 == 0) { s_l[j] = lrun; s_m[j] = mrun; }
     __syncthreads();
     if (j == 0) {
-        float num = 0.f, den = 0.f;
-#pragma unroll
-        for (int q = 0; q < kCombineLanes; q++) {
-            num += s_acc[q][d];
-            den += s_l[q];
+        float mmax = s_m[0];
+        for (int q = 1; q < lanes; q++) mmax = fmaxf(mmax, s_m[q]);
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+        float den = 0.f;
+        for (int q = 0; q < lanes; q++) {
+            const float w = s_m[q] == -INFINITY ? 0.f : exp2f(s_m[q] - mmax);
+            const float4 v = s_acc[q][d4];
+            num.x += w * v.x; num.y += w * v.y; num.z += w * v.z; num.w += w * v.w;
+            den += w * s_l[q];
         }
+        const float inv = 1.f / den;
         const int gq = m / a.rows, r = m - gq * a.rows;
-        a.out[((int64_t)r * a.hq + kvh * a.group + gq) * 128 + d] = __float2half_rn(num / den);
+        uint2 ov;
+        ov.x = pack_h2(num.x * inv, num.y * inv);
+        ov.y = pack_h2(num.z * inv, num.w * inv);
+        *reinterpret_cast<uint2*>(a.out + ((int64_t)r * a.hq + kvh * a.group + gq) * 128 + 4 * d4) = ov;
     }
 }
 
@@ -492,6 +504,6 @@ extern "C" int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, cons
         default: rc = launch_attn_partial<8>(a, s, pdl); break;
     }
     if (rc) return rc;
-    return launch_kernel(attn_combine_kernel, dim3((unsigned)m, (unsigned)kv_heads), dim3(128 * kCombineLanes), 0, s,
-                         pdl, a);
+    const int lanes = std::min(kCombineMaxLanes, std::max(4, (a.nsplit + 3) / 4));
+    return launch_kernel(attn_combine_kernel, dim3((unsigned)m, (unsigned)kv_heads), dim3(32 * lanes), 0, s, pdl, a);
 }
