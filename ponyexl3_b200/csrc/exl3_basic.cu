@@ -97,22 +97,25 @@ __global__ void __launch_bounds__(256)
     // weights right away; it waits for this grid before it reads any activation.
     griddep_launch_dependents();
     if (wait_dependency) griddep_wait();
+    // 32-bit block arithmetic (the launcher refuses more than 2^31 blocks): the 64-bit divisions
+    // that split a block index into (row, block of the row) cost more than the butterfly itself
     const int lane = threadIdx.x & 31;
-    const int64_t nblk = n >> 7;
-    const int64_t total = rows * nblk;
-    const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    const uint32_t nblk = (uint32_t)(n >> 7);
+    const uint32_t total = (uint32_t)rows * nblk;
+    const uint32_t warp0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t nwarps = gridDim.x * (blockDim.x >> 5);
     // Four 128-blocks per warp and turn: the loads of all four are in flight before the first
     // butterfly starts (one 256-byte load per warp at a time left the kernel latency-bound).
     constexpr int U = 4;
-    for (int64_t i0 = warp0; i0 < total; i0 += nwarps * U) {
+    for (uint32_t i0 = warp0; i0 < total; i0 += nwarps * U) {
         float v[U][4], sp[U][4];
         int64_t rr[U], cc[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            const int64_t i = i0 + u * nwarps;       // strided: small problems still use every warp
-            const bool ok = i < total;
-            const int64_t r = ok ? i / nblk : 0, b = ok ? i % nblk : 0;
+            const uint32_t i = i0 + u * nwarps;      // strided: small problems still use every warp
+            const bool ok = i < total && i >= i0;    // (i >= i0: no wrap-around)
+            const uint32_t rq = ok ? i / nblk : 0u;
+            const int64_t r = rq, b = ok ? i - rq * nblk : 0u;
             rr[u] = ok ? r : -1;
             cc[u] = b * 128 + lane * 4;
             const int64_t rs = row_src ? row_src[r] : r;
@@ -240,6 +243,7 @@ int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t
                     const int32_t* pre_row, const int32_t* post_row, bool pdl, int out_mode,
                     cudaStream_t s)
 {
+    if (rows * (n >> 7) >= ((int64_t)1 << 31)) return EXL3_E_RANGE;   // the kernel counts blocks in 32 bits
     const int g = grid_for(rows * (n >> 7), 8);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(g);
