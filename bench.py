@@ -290,7 +290,7 @@ def run_gpu(args):
 
     def one_layer(L, x):
         if dist is None:
-            ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=True, out=L.y)
+            ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=True, out=L.y, fast_accum=args.fast_accum)
         elif peer is not None:
             L.y_full = ops.gemv_peers(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, exchange=peer,
                                       out_features_total=L.outf, col0=L.c0, pdl=True)
@@ -449,6 +449,7 @@ def run_gpu(args):
                 "workload": "configs[1]: batch-1 GEMV, K=4, 3INST, shapes 5120x17408 + 17408x5120 + "
                             "5120x5120",
                 "rows": ROWS, "k": K_BITS, "codebook": "3INST", "ring_sets": args.ring,
+                "accumulate": "fast" if args.fast_accum else "exact",
                 "step_packed_bytes": step_bytes_global,
                 "l2": f"inputs larger than L2: {step_bytes_global / world / 1e6:.0f} MB of distinct "
                       f"weights per GPU per step vs 126 MB L2",
@@ -876,6 +877,9 @@ def main():
     ap.add_argument("--nccl-gather", action="store_true",
                     help="N > 1: NCCL all-gather per layer instead of the peer-memory epilogue")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--fast-accum", action="store_true",
+                    help="gemv workload, 1 GPU: EXL3_FLAG_FAST_ACCUM (the two fp16 halves of a codebook value "
+                         "are added inside the fp32 accumulation; outputs move by about 4e-4 relative)")
     ap.add_argument("--profile-case", choices=["gemv", "gemm"], default=None,
                     help="run one small case for an ncu capture and exit")
     ap.add_argument("--sweep", action="store_true",

@@ -99,8 +99,12 @@ EXL3_API int exl3_hadamard128(const void* x, int x_dtype, int64_t rows, int64_t 
 
 /* Bytes of scratch the matmul entry points need for activations of up to `max_rows` rows
  * (counting every member of a sibling group and every MoE slot) and `max_in` input
- * features.  The caller allocates it (256-byte aligned) and calls exl3_workspace_init once
- * before first use; calls that share a workspace must be ordered on one stream. */
+ * features: a status word, the arrival counters and fp32 partial sums of column blocks that
+ * the streamed GEMV splits over several CTAs, and the rotated activations.  The caller
+ * allocates it (256-byte aligned) and calls exl3_workspace_init once before first use (the
+ * counters must start at zero; every launch leaves them at zero); calls that share a
+ * workspace must be ordered on one stream.  A workspace larger than asked for is fine; one
+ * that is smaller but still holds the activations only makes the GEMV use fewer CTAs. */
 EXL3_API size_t exl3_workspace_bytes(int64_t max_rows, int64_t max_in);
 EXL3_API int exl3_workspace_init(void* workspace, size_t bytes, exl3_stream_t stream);
 /* Device-side status word of the workspace (0 = no kernel reported a bounded wait giving
@@ -178,8 +182,9 @@ EXL3_API int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, i
  * forbidden or all free memory already belongs to someone else's pool.
  * This entry point has no counterpart in the reference (unified memory there makes the
  * question moot); it is an addition of this library.
- *   - The scratch (status word + rotated activations) is a fixed device array inside the
- *     library, 1 MiB + 256 B per GPU, held from library load until the process exits.
+ *   - The scratch (status word, split-block counters and partial sums, rotated activations)
+ *     is a fixed device array inside the library, 5.75 MiB + 2304 B per GPU, held from
+ *     library load until the process exits.
  *   - Limit: rows * in_features <= 262,144 (e.g. 16 rows x 16,384 features); larger calls
  *     return EXL3_E_RANGE and launch nothing.
  *   - The first call on each device looks up the array's device address; make that first
@@ -194,6 +199,10 @@ EXL3_API int exl3_gemv_noalloc(const void* x, int x_dtype, int rows, int64_t x_r
                                const uint16_t* suh, const uint16_t* svh, const uint16_t* bias,
                                uint16_t* y, int64_t y_row_stride, unsigned flags,
                                exl3_stream_t stream);
+/* Status word of that built-in scratch (the caller never sees the array, so
+ * exl3_workspace_status cannot be used): 0 = no bounded wait of an exl3_gemv_noalloc kernel
+ * ever gave up on this device.  Synchronises the stream.  No counterpart in the reference. */
+EXL3_API int exl3_gemv_noalloc_status(int* status_out, exl3_stream_t stream);
 
 /* ---- the caller's side of a decode step --------------------------------------------------
  * What sits between the EXL3 linears of a transformer layer during generation.  The reference
@@ -245,8 +254,8 @@ EXL3_API int exl3_swiglu(const uint16_t* gate_up, int64_t gu_row_stride, uint16_
  * exl3_peer_allgather: the same exchange for a (rows, cols) slice computed by other kernels;
  *   one arrival per rank, so the full row is complete after n_peers arrivals.
  * exl3_peer_wait: one-thread kernel that polls this rank's counter until `target` arrivals are
- *   there, subtracts them again and ends.  The poll gives up after about a second and sets bit 16
- *   in the status word of `workspace` (exl3_workspace_status).  A (buffer, counter) pair must not be
+ *   there, subtracts them again and ends.  The poll gives up after about a second and sets the
+ *   value 16 (mask 0x10) in the status word of `workspace` (exl3_workspace_status).  A (buffer, counter) pair must not be
  *   the target of two consecutive exchanges: rotate over at least two pairs. */
 EXL3_API int exl3_gemv_peers(const void* x, int x_dtype, int rows, int64_t x_row_stride,
                              const uint16_t* trellis, int64_t t_in, int64_t t_out, int k, int cb,

@@ -1,0 +1,27 @@
+/*
+ * exl3_b200_tuning — benchmark knobs of libexl3b200.so, outside the stable ABI of exl3_b200.h.
+ *
+ * These set process-wide state that every later streamed-GEMV launch reads; they exist for
+ * sweeps that look for the best launch shape and are never called on a product path.  They have
+ * no counterpart in the reference.
+ */
+#ifndef EXL3_B200_TUNING_H
+#define EXL3_B200_TUNING_H
+
+#include "exl3_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* max_grid: largest number of virtual CTAs (halves of the 1024-thread CTAs) a streamed GEMV
+ * deals its items to (0 = two per SM, the default);
+ * fuse_x_bytes: the input rotation runs inside the GEMV when the rotated words of one half fit in
+ * this many bytes of shared memory, 0 .. 28,672 (values outside leave it as it is; the default
+ * is the maximum; 0 always uses the separate rotation kernel). */
+EXL3_API void exl3_tune_gemv(int max_grid, int fuse_x_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXL3_B200_TUNING_H */

@@ -52,6 +52,7 @@ _PROTOTYPES = {
     "exl3_gemv_noalloc": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int,
                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_uint,
                                   c_void_p]),
+    "exl3_gemv_noalloc_status": (c_int, [ctypes.POINTER(c_int), c_void_p]),
     "exl3_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
                                  c_int64, ctypes.c_float, c_uint, c_void_p]),
     "exl3_rope_append": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -66,6 +67,7 @@ _PROTOTYPES = {
     "exl3_peer_allgather": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64,
                                     c_int64, c_uint, c_void_p]),
     "exl3_peer_wait": (c_int, [c_void_p, c_uint, c_void_p, c_uint, c_void_p]),
+    "exl3_tune_gemv": (None, [c_int, c_int]),
     "exl3_moe_prefill_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
     "exl3_moe_decode_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,
@@ -73,6 +75,15 @@ _PROTOTYPES = {
 }
 
 _lib: ctypes.CDLL | None = None
+
+
+def use_library(path: Path) -> None:
+    """Bind another build of the library (the timeline build of ``ponyexl3_b200.profiling``).
+    Must be called before the first ``load()``."""
+    global LIB_PATH
+    if _lib is not None:
+        raise RuntimeError("the library is already loaded")
+    LIB_PATH = Path(path)
 
 
 def load() -> ctypes.CDLL:

@@ -42,19 +42,26 @@ def _deps_mtime() -> float:
     return max(p.stat().st_mtime for p in hdrs)
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile what changed and link; returns the library path."""
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False,
+          profile: bool = False) -> Path:
+    """Compile what changed and link; returns the library path.
+
+    ``profile=True`` builds a second library, ``lib/libexl3b200_prof.so``, with -DEXL3_PROFILE:
+    the streamed GEMV then records wall-clock stamps per CTA (``ponyexl3_b200.profiling``).  The
+    product library is never built with that flag."""
     LIBDIR.mkdir(exist_ok=True)
-    OBJDIR.mkdir(exist_ok=True)
+    objdir = OBJDIR / "prof" if profile else OBJDIR
+    objdir.mkdir(exist_ok=True, parents=True)
+    lib = LIBDIR / "libexl3b200_prof.so" if profile else LIB
     nvcc = _nvcc()
     hdr_t = _deps_mtime()
     jobs = []
     objs = []
     for src in sources():
-        obj = OBJDIR / (src.stem + ".o")
+        obj = objdir / (src.stem + ".o")
         objs.append(obj)
         if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_t):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *NVCC_FLAGS, *(["-DEXL3_PROFILE"] if profile else []), "-c", str(src), "-o", str(obj)]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)
@@ -64,18 +71,19 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if ptxas_info and r.stderr:
-            (OBJDIR / (Path(cmd[-3]).stem + ".ptxas.txt")).write_text(r.stderr)
+            (objdir / (Path(cmd[-3]).stem + ".ptxas.txt")).write_text(r.stderr)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
 
     if jobs:
         with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
             list(ex.map(run, jobs))
-    if jobs or not LIB.exists():
-        run([nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"])
-    return LIB
+    if jobs or not lib.exists():
+        run([nvcc, "-shared", "-o", str(lib), *map(str, objs), "-lcudart"])
+    return lib
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv,
+              profile="--profile" in sys.argv)
     print(p)

@@ -126,6 +126,25 @@ EXL3_HD void lane_codewords_k4(uint32_t w, uint32_t prev, uint32_t (&cw)[8], uin
     cw[0] = hi4;
 }
 
+// Same, with the two windows that are 16-bit aligned inside the lane's word handed in: w_lo =
+// w & 0xFFFF (codeword 7) and w_hi = w >> 16 (codeword 3).  A kernel reads them with 16-bit
+// shared-memory loads, which takes two byte permutes per tile off the logic pipe.
+EXL3_HD void lane_codewords_k4_halves(uint32_t w, uint32_t prev, uint32_t w_lo, uint32_t w_hi,
+                                      uint32_t (&cw)[8], uint32_t sixteen = 16u)
+{
+    const uint32_t p = prev & 0xFFFu;
+    uint32_t lo4, hi4;
+    mad_wide(w, sixteen, p * sixteen, lo4, hi4);
+    cw[7] = w_lo;
+    cw[5] = byte_perm(w, 0u, 0x4421);
+    cw[3] = w_hi;
+    cw[1] = byte_perm(w, p, 0x6643);
+    cw[6] = byte_perm(lo4, 0u, 0x4421);
+    cw[4] = byte_perm(lo4, 0u, 0x4432);
+    cw[2] = byte_perm(lo4, hi4, 0x6643);
+    cw[0] = hi4;
+}
+
 // Integer part of the codebooks (reference: ponyexl3/ref/codebook.py:66-91).
 // 3INST and MCG: a 32-bit word whose two fp16 halves sum to the weight.
 // MUL1: the fp16 bit pattern 0x6400 + (sum of the product's bytes), to be sent

@@ -1,10 +1,12 @@
 // extern "C" surface of libexl3b200.so: argument validation on the host, then the
-// kernel launchers.  No allocation, no global mutable state beyond per-device
-// caches of immutable facts (SM count, function attributes).
+// kernel launchers.  No allocation; the only process-wide state is per-device caches of
+// immutable facts (SM count, function attributes) and the two benchmark knobs of
+// exl3_b200_tuning.h, which no product path sets.
 #include <stdio.h>
 #include <string.h>
 
 #include "exl3_internal.h"
+#include "../../include/exl3_b200_tuning.h"
 #include "exl3_tma.h"
 
 namespace exl3 {
@@ -68,9 +70,9 @@ int check_launch() { return note_cuda(cudaGetLastError()); }
 
 int device_sm_count()
 {
-    static int cached[64] = {};
+    static int cached[kMaxDevices] = {};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
     if (cached[dev] == 0) {
         int n = 0;
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
@@ -80,8 +82,17 @@ int device_sm_count()
     return cached[dev];
 }
 
-void gemv_set_tuning(int ctas_per_sm, int smem_budget_bytes);
-void gemv_force_split(int ksplit);
+#ifdef EXL3_PROFILE
+// Timeline builds only: a caller-owned device buffer that consecutive GEMV launches fill with
+// per-CTA time stamps, kGemvMaxGrid x 16 x 8 bytes per launch, until it is full.
+static long long* g_prof_buf = nullptr;
+static size_t g_prof_launches = 0, g_prof_next = 0;
+static long long* next_prof_slot()
+{
+    if (!g_prof_buf || g_prof_next >= g_prof_launches) return nullptr;
+    return g_prof_buf + (g_prof_next++) * (size_t)kGemvMaxGrid * 16;
+}
+#endif
 
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
@@ -176,13 +187,18 @@ int exl3_hadamard128(const void* x, int x_dtype, int64_t rows, int64_t n, int64_
                            nullptr, nullptr, nullptr, false, HAD_OUT_F16, (cudaStream_t)stream);
 }
 
+// Where the partial sums of split column blocks start: after the rotated activations (one word
+// per element), on a 256-byte boundary.
+static size_t gemv_partial_offset(int64_t xh_rows, int64_t in)
+{
+    return (kWsScratch + (size_t)xh_rows * (size_t)in * 4 + 255) & ~(size_t)255;
+}
+
 size_t exl3_workspace_bytes(int64_t max_rows, int64_t max_in)
 {
     if (max_rows < 1) max_rows = 1;
     if (max_in < 128) max_in = 128;
-    size_t b = kWsScratch;
-    b += (size_t)max_rows * (size_t)max_in * 4;  // rotated activations, one word per element
-    return (b + 255) & ~(size_t)255;
+    return gemv_partial_offset(max_rows, max_in) + gemv_partial_bytes((int)(max_rows < 16 ? max_rows : 16));
 }
 
 int exl3_workspace_init(void* workspace, size_t bytes, exl3_stream_t stream)
@@ -230,8 +246,9 @@ static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_strid
         return EXL3_E_ALIGN;
     if (!workspace) return EXL3_E_WORKSPACE;
     if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
-    const size_t need = kWsScratch + (size_t)rows * in * 4;
-    if (workspace_bytes < need) return EXL3_E_WORKSPACE;
+    const size_t part_off = gemv_partial_offset(rows, in);
+    if (workspace_bytes < part_off + (size_t)rows * kGemvPartialBytesPerCtaRow) return EXL3_E_WORKSPACE;
+    const size_t part_bytes = workspace_bytes - part_off;
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     uint32_t* xh = reinterpret_cast<uint32_t*>(ws + kWsScratch);
@@ -239,7 +256,7 @@ static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_strid
     const bool fast = (flags & EXL3_FLAG_FAST_ACCUM) != 0 && cb != CB_MUL1;
     cudaStream_t s = (cudaStream_t)stream;
 
-    const bool x_fused = gemv_x_is_fused(rows, (int)t_in, (int)(t_out / 8));
+    const bool x_fused = gemv_x_is_fused(rows, (int)t_in, t_out / 8, false, part_bytes);
     if (!x_fused) {
         rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
                              nullptr, reinterpret_cast<__half*>(xh), nullptr, nullptr, nullptr, pdl,
@@ -268,11 +285,11 @@ static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_strid
     a.x_row_stride = x_row_stride;
     a.x_dtype = x_dtype;
     a.x_fused = x_fused ? 1 : 0;
+    a.partials = reinterpret_cast<float*>(ws + part_off);
+    a.partial_bytes = part_bytes;
+    a.split_ctr = reinterpret_cast<unsigned*>(ws + kWsSplitCtr);
 #ifdef EXL3_PROFILE
-    {   // timing builds reuse the scratch area; consecutive launches alternate between two slots
-        static int prof_launch = 0;
-        a.prof = reinterpret_cast<long long*>(ws + kWsScratch) + (size_t)(prof_launch++ & 1) * 400 * 16 * 16;
-    }
+    a.prof = next_prof_slot();
 #endif
     a.n_peer = peer.n;
     a.y_col0 = peer.col0;
@@ -341,7 +358,9 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
         return EXL3_E_ALIGN;
     if (!workspace) return EXL3_E_WORKSPACE;
     if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
-    if (workspace_bytes < kWsScratch + (size_t)xh_rows * in * 4) return EXL3_E_WORKSPACE;
+    const size_t part_off = gemv_partial_offset(xh_rows, in);
+    if (workspace_bytes < part_off + (size_t)rows * kGemvPartialBytesPerCtaRow) return EXL3_E_WORKSPACE;
+    const size_t part_bytes = workspace_bytes - part_off;
     if (n_blocks == 0) return EXL3_OK;
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -349,9 +368,9 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
     const bool pdl = (flags & EXL3_FLAG_PDL) != 0;
     const bool fast = (flags & EXL3_FLAG_FAST_ACCUM) != 0 && cb != CB_MUL1;
     cudaStream_t s = (cudaStream_t)stream;
-    // One block per cluster and few rows: the kernel rotates its own row; else a rotation kernel
-    // fills the workspace first.
-    const bool x_fused = gemv_blocks_x_is_fused(rows, (int)t_in, (int)n_blocks);
+    // Few rows and short item ranges: the kernel rotates the rows of its own blocks; else a
+    // rotation kernel fills the workspace first.
+    const bool x_fused = gemv_x_is_fused(rows, (int)t_in, n_blocks, true, part_bytes);
     if (!x_fused) {
         rc = launch_hadamard(x, x_dtype, xh_rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
                              nullptr, reinterpret_cast<__half*>(xh), row_src, suh_row, nullptr, pdl,
@@ -381,6 +400,10 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
     a.x_fused = x_fused ? 1 : 0;
     a.row_src = row_src;
     a.suh_row = suh_row;
+    a.partials = reinterpret_cast<float*>(ws + part_off);
+    a.partial_bytes = part_bytes;
+    a.split_ctr = reinterpret_cast<unsigned*>(ws + kWsSplitCtr);
+    a.done_ctr = reinterpret_cast<unsigned*>(ws + kWsDoneCtr);
     return launch_gemv(a, k, cb, pdl, s);
 }
 
@@ -482,17 +505,21 @@ int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh
     return launch_gemm(a, k, cb, xh, reinterpret_cast<const uint32_t*>(trellis), s);
 }
 
-/* Tuning hook used by the benchmark sweeps: CTAs per SM (1 or 2) and the dynamic
- * shared-memory budget per CTA of the streamed GEMV.  Not part of the stable ABI. */
-EXL3_API void exl3_tune_gemv(int ctas_per_sm, int smem_budget_bytes)
+#ifdef EXL3_PROFILE
+/* Timeline builds only (python -m ponyexl3_b200.build --profile): hand in a zeroed device buffer of
+ * launches x 512 x 128 bytes; the next `launches` exl3_gemv calls each fill one slot with 16 words
+ * per CTA (see the end of gemv_kernel). */
+EXL3_API void exl3_profile_buffer(void* buf, size_t launches)
 {
-    gemv_set_tuning(ctas_per_sm, smem_budget_bytes);
+    g_prof_buf = static_cast<long long*>(buf);
+    g_prof_launches = launches;
+    g_prof_next = 0;
 }
+#endif
 
-/* Same kind of hook: force the k-split (CTAs per cluster) of the streamed GEMV; 0 = automatic. */
-EXL3_API void exl3_tune_gemv_split(int ksplit)
+void exl3_tune_gemv(int max_grid, int fuse_x_bytes)
 {
-    gemv_force_split(ksplit);
+    gemv_set_tuning(max_grid, fuse_x_bytes);
 }
 
 }  // extern "C"

@@ -1,5 +1,5 @@
-// Host-side dispatch of the streamed GEMV: tuning knobs, the k-split choice, and the switch
-// over K.  The kernel template lives in exl3_gemv.cuh and is instantiated once per K in
+// Host-side dispatch of the streamed GEMV: the launch plan (grid, fused rotation or not) and the
+// switch over K.  The kernel template lives in exl3_gemv.cuh and is instantiated once per K in
 // exl3_gemv_k{1..8}.cu so the eight translation units compile in parallel.
 #include <algorithm>
 
@@ -7,88 +7,92 @@
 
 namespace exl3 {
 
-int g_gemv_ctas_per_sm = 2;
-int g_gemv_smem_budget = 110 * 1024;
-static int g_fuse_x_bytes = 40 * 1024;   // fuse the input rotation when its words fit in this
+constexpr int kCtasPerSm = 2;           // virtual CTAs: the two halves of the one real CTA per SM
+static int g_fuse_x_bytes = 28 * 1024;   // fuse the input rotation when a half's words fit in this
 constexpr int kXsRowBytesHost = 544;
 
-static int g_cluster_cache[16][9] = {};
+static int g_gemv_max_grid = 0;          // 0: two virtual CTAs per SM
+static bool g_gemv_search_grid = true;
 
-void gemv_set_tuning(int ctas_per_sm, int smem_budget_bytes)
+// Benchmark hook (exl3_b200_tuning.h): cap the grid and the size of the fused-rotation buffer.
+void gemv_set_tuning(int max_grid, int fuse_x_bytes)
 {
-    if (ctas_per_sm >= 1 && ctas_per_sm <= 2) g_gemv_ctas_per_sm = ctas_per_sm;
-    if (smem_budget_bytes >= 32 * 1024 && smem_budget_bytes <= 226 * 1024)
-        g_gemv_smem_budget = smem_budget_bytes;
-    for (auto& row : g_cluster_cache)
-        for (int& v : row) v = 0;
+    g_gemv_max_grid = max_grid > 0 ? std::min(max_grid, kGemvMaxGrid) : 0;
+    g_gemv_search_grid = max_grid == 0;      // a forced count is taken as it is
+    if (fuse_x_bytes >= 0 && fuse_x_bytes <= 28 * 1024) g_fuse_x_bytes = fuse_x_bytes;
 }
 
-static int g_force_split = 0;
-void gemv_force_split(int ksplit) { g_force_split = (ksplit >= 1 && ksplit <= 8) ? ksplit : 0; }
-
-int gemv_active_clusters_probe(int cluster, int smem_bytes);   // exl3_gemv_k4.cu
-
-// Clusters of s CTAs that are resident at once (a cluster must fit inside one GPC, so this
-// is not slots / s: e.g. clusters of 7 leave a remainder in every GPC).  Cached per device.
-static int active_clusters(int s)
+size_t gemv_partial_bytes(int rows)
 {
-    int (&cache)[16][9] = g_cluster_cache;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 16) dev = 0;
-    if (cache[dev][s] == 0) {
-        int n = s == 1 ? device_sm_count() * g_gemv_ctas_per_sm
-                       : gemv_active_clusters_probe(s, g_gemv_smem_budget);
-        if (n <= 0) n = std::max(1, device_sm_count() * g_gemv_ctas_per_sm / s / 2);
-        n = std::min(n, std::max(1, device_sm_count() * g_gemv_ctas_per_sm / s));
-        cache[dev][s] = n;
-    }
-    return cache[dev][s];
+    return (size_t)kGemvMaxGrid * (size_t)rows * kGemvPartialBytesPerCtaRow;
 }
 
-// k-split S and grid for a layer.  Time is proportional to (waves of clusters) x (k-blocks
-// per CTA); pick the S that minimises it, preferring the smaller S on ties.
-// The leader keeps (S - 1) x rows x 128 floats of landing slots for the others' partial sums;
-// S is capped so that they stay under 24 KiB.
-void gemv_choose_split(int ncb, int nkb, int rows, int* ksplit, int* grid)
+// Cost of dealing the items to g virtual CTAs, in item times of one warp group: the slowest
+// virtual CTA sets the launch time; each of its segments costs its rounds (four groups, one item
+// each per round) plus a hand-over of the partial sums, which stalls the half for most of an item
+// time.
+static double plan_cost(int64_t ncb, int nkb, int g)
 {
-    int best_s = 1, best_clusters = 1;
-    long best_t = -1;
-    const int s_max = std::min(std::min(8, nkb), 1 + 24576 / (rows * 512));
-    const int s_lo = g_force_split ? std::min(g_force_split, s_max) : 1;
-    const int s_hi = g_force_split ? s_lo : s_max;
-    for (int s = s_lo; s <= s_hi; s++) {
-        const int clusters = std::min(ncb, active_clusters(s));
-        const long waves = (ncb + clusters - 1) / clusters;
-        const long t = waves * ((nkb + s - 1) / s) * 16 + s;   // + s: cost of gathering s partial sums
-        if (best_t < 0 || t < best_t) {
-            best_t = t;
-            best_s = s;
-            best_clusters = clusters;
+    const int64_t items = ncb * nkb;
+    double worst = 0;
+    for (int c = 0; c < g; c++) {
+        int64_t i0 = items * c / g;
+        const int64_t i1 = items * (c + 1) / g;
+        double t = 0;
+        while (i0 < i1) {
+            const int64_t end = std::min(i1, (i0 / nkb + 1) * nkb);
+            t += (double)((end - i0 + 3) / 4) + 0.8;
+            i0 = end;
         }
+        worst = std::max(worst, t);
     }
-    *ksplit = best_s;
-    *grid = best_clusters * best_s;
+    return worst;
 }
 
-bool gemv_x_is_fused(int rows, int t_in, int ncb)
+// The items (column blocks x k-blocks) are dealt out evenly to `grid` virtual CTAs (two per SM:
+// the halves of the real CTA), fewer when the layer has fewer items or the caller's partial-sum
+// area holds fewer.  Among the counts down to three quarters of the largest one the cheapest by
+// plan_cost is taken: a count that lets ranges end on block boundaries (136 column blocks on 272
+// of 296 halves) saves more by avoiding second segments than it loses in idle SMs.  The choice
+// is remembered per shape.
+GemvPlan gemv_plan(int64_t ncb, int nkb, int rows, bool table, size_t partial_bytes)
 {
-    if (rows > 8) return false;
-    int s, grid;
-    gemv_choose_split(ncb, t_in >> 3, rows, &s, &grid);
-    const int nkb = t_in >> 3;
-    const int klen = (nkb + s - 1) / s;
-    return (klen * rows + 1) * kXsRowBytesHost <= g_fuse_x_bytes;
+    GemvPlan p = {};
+    const int64_t items = ncb * nkb;
+    int64_t grid = std::min<int64_t>(kGemvMaxGrid, (int64_t)device_sm_count() * kCtasPerSm);
+    if (g_gemv_max_grid > 0) grid = std::min<int64_t>(grid, g_gemv_max_grid);
+    grid = std::min<int64_t>(grid, (int64_t)(partial_bytes / ((size_t)rows * kGemvPartialBytesPerCtaRow)));
+    grid = std::min(grid, items);
+    p.grid = (int)std::max<int64_t>(grid, 0);
+    if (p.grid < 1) return p;
+    if (g_gemv_search_grid && p.grid >= 16 && ncb <= (1 << 16)) {
+        struct Memo { int64_t ncb; int nkb, gmax, best; };
+        static thread_local Memo memo[16] = {};
+        static thread_local int memo_next = 0;
+        int best = 0;
+        for (const Memo& m : memo)
+            if (m.ncb == ncb && m.nkb == nkb && m.gmax == p.grid) best = m.best;
+        if (!best) {
+            double best_cost = 0;
+            for (int g = p.grid; g >= p.grid - p.grid / 4; g--) {
+                const double cst = plan_cost(ncb, nkb, g);
+                if (!best || cst < best_cost - 1e-9) { best = g; best_cost = cst; }
+            }
+            memo[memo_next] = Memo{ncb, nkb, p.grid, best};
+            memo_next = (memo_next + 1) % 16;
+        }
+        p.grid = best;
+    }
+    const int64_t range = (items + p.grid - 1) / p.grid;         // longest item range of a virtual CTA
+    const int64_t slots = table ? range : std::min<int64_t>(range, nkb);
+    p.n_slots = (int)std::min<int64_t>(slots, 1 << 20);
+    p.x_fused = rows <= 8 && (slots * rows + 1) * kXsRowBytesHost <= g_fuse_x_bytes;
+    return p;
 }
 
-// A block-table launch can rotate its activations in the kernel when every cluster computes a
-// single block: the CTA then needs one (rotated row, sign vector) pair for its whole life.
-bool gemv_blocks_x_is_fused(int rows, int t_in, int ncb)
+bool gemv_x_is_fused(int rows, int t_in, int64_t ncb, bool table, size_t partial_bytes)
 {
-    if (!gemv_x_is_fused(rows, t_in, ncb)) return false;
-    int s, grid;
-    gemv_choose_split(ncb, t_in >> 3, rows, &s, &grid);
-    return ncb <= grid / s;
+    return gemv_plan(ncb, t_in >> 3, rows, table, partial_bytes).x_fused;
 }
 
 template <int K> int launch_gemv_k(const GemvArgs& a, int cb, bool pdl, cudaStream_t s);

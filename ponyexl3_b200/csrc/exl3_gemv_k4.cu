@@ -3,8 +3,4 @@
 
 namespace exl3 {
 template int launch_gemv_k<4>(const GemvArgs&, int, bool, cudaStream_t);
-int gemv_active_clusters_probe(int cluster, int smem_bytes)
-{
-    return gemv_query_active_clusters<4>(cluster, smem_bytes);
-}
 }

@@ -32,13 +32,25 @@ inline int launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t s
     return note_cuda(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
 }
 
+// Per-device caches of immutable facts (function attributes, SM count) are arrays of this size;
+// a device index beyond it is refused with EXL3_E_UNSUPPORTED.
+constexpr int kMaxDevices = 64;
+
 // ---- workspace layout ------------------------------------------------------------------------
-// [0, 256)      status word + padding (zero = no bounded wait ever gave up)
-// [256, ...)    scratch: the rotated activations xh of the current call — one 32-bit word per
-//               element for the GEMV when the rotation is not fused, fp16 for the GEMM
+// [0, 256)        status word + padding (zero = no bounded wait ever gave up)
+// [256, 2304)     arrival counters of the streamed GEMV's split column blocks (one per CTA of the
+//                 largest grid); zero between launches: the CTA that completes a count resets it
+// [2304, ...)     scratch: the rotated activations xh of the current call — one 32-bit word per
+//                 element for the GEMV when the rotation is not fused, fp16 for the GEMM
+// after xh        GEMV only: fp32 partial sums of split column blocks, two slots of rows x 128
+//                 floats per CTA (exl3_workspace_bytes reserves kGemvMaxGrid CTAs; a smaller
+//                 area only shrinks the grid)
 constexpr size_t kWsStatus = 0;
 constexpr size_t kWsDoneCtr = 64;   // finished-block counter of a launch with peer outputs (inside the status area)
-constexpr size_t kWsScratch = 256;
+constexpr size_t kWsSplitCtr = 256;
+constexpr int kGemvMaxGrid = 512;
+constexpr size_t kWsScratch = kWsSplitCtr + 4 * (size_t)kGemvMaxGrid;
+constexpr size_t kGemvPartialBytesPerCtaRow = 2 * 128 * 4;   // two slots of 128 floats
 
 // ---- launchers -------------------------------------------------------------------------------
 int launch_unpack(const uint32_t* trellis, int64_t n_tiles, int k, uint16_t* out, cudaStream_t s);
@@ -77,7 +89,6 @@ struct GemvArgs {
     int ncb;                   // logical 128-column blocks to compute
     int rows;                  // activation rows per block (1..16)
     int x_rows_total;          // rows of the xh matrix (>= xrow + rows of every block)
-    int stages;                // depth of the shared-memory ring
     int raw_out;               // 1: write fp16(y_inner) without rotation (MoE gate/up)
     int fast_accum;
     // fused input rotation (few rows): the kernel reads x itself
@@ -88,13 +99,19 @@ struct GemvArgs {
     int x_fused;               // 1: rotate x in the kernel; 0: xh was written by the rotation kernel
     const int32_t* row_src;    // fused rotation of a block-table launch: x row of rotated row i (NULL: i)
     const int32_t* suh_row;    // ... and its row of the stacked suh matrix (NULL: row 0)
+    // split column blocks: partial sums and arrival counters in the workspace
+    float* partials;           // two slots of rows x 128 floats per CTA
+    size_t partial_bytes;      // size of that area (bounds the grid)
+    unsigned* split_ctr;       // kGemvMaxGrid counters, zero between launches
+    long long* prof;           // timeline builds: 8 stamps per CTA of this launch; NULL otherwise
     // filled in by the launcher
-    long long* prof;           // EXL3_PROFILE builds: per-warp cycle counters; NULL otherwise
     uint32_t sixteen;          // the number 16 as a run-time value (keeps shifts on the multiplier)
     uint32_t cb_xor;           // XOR constant of the 3INST / MCG codebooks, as a run-time value
-    int ksplit;                // CTAs per cluster = k-slices per column block
+    int grid_virtual;          // virtual CTAs (halves of real CTAs) the items are dealt to
+    int xs_bytes;              // fused rotation: bytes of rotated activations per half
+    int n_slots;               // fused rotation: k-block slots of rotated activations per CTA
+    int stages;                // depth of the shared-memory ring
     int stage0_off;            // byte offset of the ring inside dynamic shared memory
-    int slot_off;              // byte offset of the leader's landing slots for the other CTAs' partial sums
     // output all-gather over peer memory (tensor parallel by output tile): when n_peer > 0 every
     // finished block is stored into each rank's full-width row buffer and announced on its counter
     int n_peer;
@@ -106,8 +123,20 @@ struct GemvArgs {
 constexpr int kMaxPeers = 8;
 
 int launch_gemv(const GemvArgs& a, int k, int cb, bool pdl, cudaStream_t s);
-bool gemv_x_is_fused(int rows, int t_in, int ncb);
-bool gemv_blocks_x_is_fused(int rows, int t_in, int ncb);   // block tables: only with one block per cluster
+// Does the GEMV rotate its activations itself (few rows, short item ranges), or does a rotation
+// kernel have to fill xh first?  `table`: the launch goes through a block table.
+bool gemv_x_is_fused(int rows, int t_in, int64_t ncb, bool table, size_t partial_bytes);
+// Bytes of the partial-sum area that let a launch with `rows` rows use the largest grid.
+size_t gemv_partial_bytes(int rows);
+// The launch plan of a streamed GEMV: the items (column blocks x k-blocks) are dealt out evenly
+// to `grid` CTAs.
+struct GemvPlan {
+    int grid;       // CTAs (0: the partial-sum area holds not even one)
+    int n_slots;    // fused rotation: k-block slots of rotated activations per CTA
+    bool x_fused;
+};
+GemvPlan gemv_plan(int64_t ncb, int nkb, int rows, bool table, size_t partial_bytes);
+void gemv_set_tuning(int max_grid, int fuse_x_bytes);   // benchmark hook, see exl3_b200_tuning.h
 
 // ---- prefill GEMM (exl3_gemm.cuh) ---------------------------------------------------------
 struct GemmArgs {

@@ -6,16 +6,19 @@
 // forbidden or too costly — inside a latency-critical decode loop, or after the process has
 // handed all free device memory to a pool it does not control.
 //
-// The scratch that exl3_gemv takes from the caller's workspace (the status word and the
-// rotated activations of the current call) lives here in a file-scope device array of fixed
-// size instead.  Every GPU that loads the library holds that array until the process exits.
+// The scratch that exl3_gemv takes from the caller's workspace (the status word, the arrival
+// counters and partial sums of column blocks split over several CTAs, and the rotated
+// activations of the current call) lives here in a file-scope device array of fixed size
+// instead.  Every GPU that loads the library holds that array until the process exits.
 #include "exl3_internal.h"
 
 namespace exl3 {
 
 // rows x in_features may not exceed this (16 rows of 16,384 features, 8 of 32,768, ...).
 constexpr size_t kNoAllocMaxElems = 262144;
-constexpr size_t kNoAllocBytes = kWsScratch + kNoAllocMaxElems * 4;   // 1 MiB + 256 B
+// Partial sums of split column blocks: room for 304 CTAs (two per SM of a 152-SM part) at 16 rows.
+constexpr size_t kNoAllocPartialBytes = 304 * 16 * kGemvPartialBytesPerCtaRow;
+constexpr size_t kNoAllocBytes = kWsScratch + kNoAllocMaxElems * 4 + kNoAllocPartialBytes;   // 5.75 MiB + 2304 B
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
@@ -59,9 +62,23 @@ extern "C" int exl3_gemv_noalloc(const void* x, int x_dtype, int rows, int64_t x
     void* scratch = nullptr;
     const int rc = noalloc_scratch(&scratch);
     if (rc) return rc;
-    // The array keeps whatever the previous call left: the rotated activations are
-    // rewritten in full by every call that reads them, and the status word is sticky on
-    // purpose (as in a caller-owned workspace), so nothing needs clearing here.
+    // The array keeps whatever the previous call left: the rotated activations and the partial
+    // sums are rewritten in full by every call that reads them, the arrival counters start at
+    // zero (zero-initialised device memory) and every launch leaves them at zero, and the
+    // status word is sticky on purpose (as in a caller-owned workspace), so nothing needs
+    // clearing here.
     return exl3_gemv(x, x_dtype, rows, x_row_stride, trellis, t_in, t_out, k, cb, suh, svh, bias, y,
                      y_row_stride, scratch, kNoAllocBytes, flags, stream);
+}
+
+// The sticky status word of the built-in scratch (0 = no bounded wait ever gave up), copied to
+// *status_out after synchronising the stream; the caller of exl3_gemv_noalloc never sees the
+// array and so cannot use exl3_workspace_status.
+extern "C" int exl3_gemv_noalloc_status(int* status_out, exl3_stream_t stream)
+{
+    if (!status_out) return EXL3_E_NULL;
+    void* scratch = nullptr;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    return exl3_workspace_status(scratch, status_out, stream);
 }

@@ -32,11 +32,17 @@ def as_u16(t: torch.Tensor) -> torch.Tensor:
 
 
 class Workspace:
-    """Per-device scratch for the matmul entry points: split-K partial sums, arrival
-    counters, the status word and the rotated activations.  One per device, grown on
-    demand; calls that share it are ordered by the stream they run on."""
+    """Per-device scratch for the matmul entry points: the status word, the arrival counters and
+    partial sums of split column blocks, and the rotated activations.  One per device, grown on
+    demand; calls that share it are ordered by the stream they run on.
+
+    A buffer that has been handed out is never freed: CUDA graphs captured earlier and work on
+    other streams keep its raw address, so when a later call needs more room a new buffer is
+    allocated and the old ones stay alive (and are still looked at by `status`).  Growth does
+    not migrate captured graphs — they keep using the buffer they were captured with."""
 
     _per_device: dict[int, "Workspace"] = {}
+    _retired: dict[int, list["Workspace"]] = {}
 
     def __init__(self, device: torch.device, nbytes: int):
         lib = _lib.load()
@@ -48,12 +54,13 @@ class Workspace:
 
     @classmethod
     def get_bytes(cls, device: torch.device, nbytes: int) -> "Workspace":
-        """The device's workspace, re-allocated (after a stream sync) when it is too small."""
+        """The device's workspace; a larger one replaces it when it is too small (the old buffer
+        stays allocated, see the class docstring)."""
         idx = device.index if device.index is not None else torch.cuda.current_device()
         ws = cls._per_device.get(idx)
         if ws is None or ws.nbytes < nbytes:
             if ws is not None:
-                torch.cuda.current_stream(device).synchronize()
+                cls._retired.setdefault(idx, []).append(ws)
             floor = int(_lib.load().exl3_workspace_bytes(16, 32768))
             ws = Workspace(torch.device("cuda", idx), max(int(nbytes), floor, ws.nbytes if ws else 0))
             cls._per_device[idx] = ws
@@ -75,12 +82,22 @@ class Workspace:
             return ws
         return cls.get_bytes(device, need)
 
-    def status(self) -> int:
+    def _status_one(self) -> int:
         import ctypes
         out = ctypes.c_int(0)
         _lib.check(_lib.load().exl3_workspace_status(self.buf.data_ptr(), ctypes.byref(out),
                                                      _stream(self.device)), "exl3_workspace_status")
         return out.value
+
+    def status(self) -> int:
+        """OR of the sticky status words of this device's workspace and of every buffer it has
+        replaced (0 = no bounded wait of any kernel ever gave up)."""
+        idx = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        st = self._status_one()
+        for old in self._retired.get(idx, []):
+            if old is not self:
+                st |= old._status_one()
+        return st
 
 
 def unpack_trellis(packed: torch.Tensor, k: int) -> torch.Tensor:
@@ -232,7 +249,7 @@ def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None
         x2d = x2d.contiguous()
     blocks = blocks.contiguous()
     lib = _lib.load()
-    ws = Workspace.get_bytes(x2d.device, 256 + xh_rows * t_in * 16 * 4)
+    ws = Workspace.get(x2d.device, xh_rows, t_in * 16)
     ptr = lambda t: None if t is None else t.data_ptr()
     _lib.check(lib.exl3_gemv_blocks(
         x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),

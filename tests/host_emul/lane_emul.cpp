@@ -45,6 +45,19 @@ extern "C" void emul_unpack_tile_k4_fast(const uint32_t* words, uint16_t* cw256)
     }
 }
 
+// Same path with the two 16-bit aligned windows read as halves of the word, as the GEMV does
+// with 16-bit shared-memory loads (little-endian: the low half comes first in memory).
+extern "C" void emul_unpack_tile_k4_halves(const uint32_t* words, uint16_t* cw256)
+{
+    const uint16_t* halves = reinterpret_cast<const uint16_t*>(words);
+    for (int lane = 0; lane < 32; lane++) {
+        uint32_t cw[8];
+        exl3::lane_codewords_k4_halves(words[lane], words[(lane + 31) & 31], halves[2 * lane],
+                                       halves[2 * lane + 1], cw);
+        for (int j = 0; j < 8; j++) cw256[lane * 8 + j] = (uint16_t)cw[j];
+    }
+}
+
 extern "C" uint32_t emul_codebook_word(int cb, uint32_t cw)
 {
     if (cb == 0) return exl3::codebook_word<exl3::CB_3INST>(cw);

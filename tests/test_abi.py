@@ -1,4 +1,4 @@
-"""The C ABI library loads and exports every symbol ``include/exl3_b200.h`` declares,
+"""The C ABI library loads and exports every symbol the headers under ``include/`` declare,
 the Python binding declares the same set, and host-side validation rejects bad
 arguments before anything touches a GPU (no compute calls here)."""
 
@@ -14,7 +14,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def _declared() -> list[str]:
-    text = (ROOT / "include" / "exl3_b200.h").read_text()
+    text = "\n".join(p.read_text() for p in sorted((ROOT / "include").glob("*.h")))
     return re.findall(r"^EXL3_API\s+[\w\s\*]+?\b(exl3_\w+)\s*\(", text, flags=re.M)
 
 

@@ -151,3 +151,44 @@ def test_config4_prefill_tile_table(cuda, oracle):
     assert ops.Workspace.get(torch.device("cuda"), 1, 128).status() == 0
     want = oracle.switch_glu(x, idx, **w, k=k, cb=0)
     assert rel_err(y.cpu().numpy().reshape(T, kk, D), want) <= 2e-3
+
+
+def test_config4_sixteen_tokens(cuda, oracle):
+    """Config-4 dims with 16 tokens x top-8 = 128 (token, slot) pairs over about 100 distinct
+    experts: the block-table GEMV with many blocks per CTA and a different sign vector per block."""
+    from ponyexl3_b200 import ops
+    from ponyexl3_b200.moe import route_topk
+
+    E, D, H, kk, k, T = 256, 2048, 512, 8, 4, 16
+    w = _experts(E, D, H, k, seed=4200)
+    sw = _switch(w, k, 0)
+    rng = np.random.default_rng(4201)
+    x = (rng.standard_normal((T, D)) * 0.02).astype(np.float16)
+    inds, _ = route_topk(torch.from_numpy(rng.standard_normal((1, T, E)).astype(np.float32)).cuda(), kk)
+    y = sw(torch.from_numpy(x).cuda().view(1, T, D), inds.view(1, T, kk))
+    assert ops.Workspace.get(torch.device("cuda"), 1, 128).status() == 0
+    want = oracle.switch_glu(x, inds.reshape(T, kk).cpu().numpy(), **w, k=k, cb=0)
+    assert rel_err(y.cpu().numpy().reshape(T, kk, D), want) <= 2e-3
+
+
+def test_config4_4096_tokens_sampled(cuda, oracle):
+    """Config-4 dims at 4096 tokens (32,768 pairs, full tile tables): every output row is finite
+    and 256 sampled (token, slot) pairs match the oracle, each pair being independent of the rest."""
+    from ponyexl3_b200 import ops
+    from ponyexl3_b200.moe import route_topk
+
+    E, D, H, kk, k, T = 256, 2048, 512, 8, 4, 4096
+    w = _experts(E, D, H, k, seed=4300)
+    sw = _switch(w, k, 0)
+    rng = np.random.default_rng(4301)
+    x = (rng.standard_normal((T, D)) * 0.02).astype(np.float16)
+    inds, _ = route_topk(torch.from_numpy(rng.standard_normal((1, T, E)).astype(np.float32)).cuda(), kk)
+    y = sw(torch.from_numpy(x).cuda().view(1, T, D), inds.view(1, T, kk))
+    assert ops.Workspace.get(torch.device("cuda"), 1, 128).status() == 0
+    y = y.cpu().numpy().reshape(T, kk, D)
+    assert np.isfinite(y.astype(np.float32)).all()
+    idx = inds.reshape(T, kk).cpu().numpy()
+    toks = rng.choice(T, size=256, replace=False)
+    slots = rng.integers(0, kk, size=256)
+    want = oracle.switch_glu(x[toks], idx[toks, slots][:, None], **w, k=k, cb=0)[:, 0]
+    assert rel_err(y[toks, slots], want) <= 2e-3

@@ -101,6 +101,59 @@ def test_config2_shapes_k4(mod, oracle, shape, rows):
     _check(mod, oracle, layer, x)
 
 
+FULL_SHAPES = [(5120, 17408), (17408, 5120), (5120, 5120)]
+
+
+@pytest.mark.parametrize("k,cb", [(k, cb) for k in (1, 3, 5, 8) for cb in (1, 2)] +
+                         [(2, 0), (5, 0), (6, 0), (7, 0)])
+def test_config2_full_shapes_other_k_and_codebooks(mod, oracle, k, cb):
+    """The sweep configuration at its real sizes away from K=4 / 3INST: one of the three
+    shapes per (K, codebook), rows 1, 8 and 16 (fused rotation, one and two MMA row groups)."""
+    inf, outf = FULL_SHAPES[(k + cb) % 3] if (k, cb) != (5, 0) else (17408, 5120)
+    layer = _layer(mod, k, inf, outf, seed=2100 + 10 * k + cb, cb=cb)
+    m = mod.EXL3Linear(layer)
+    for rows in (1, 8, 16):
+        x = np.random.default_rng(100 * k + rows).standard_normal((rows, inf)).astype(np.float16)
+        y = m(torch.from_numpy(x).cuda()).cpu().numpy()
+        want = oracle.linear_forward(x, layer.trellis, k, cb, layer.suh, layer.svh, None)
+        e = rel_err(y, want)
+        assert e <= REL_TOL, f"K={k} cb={cb} rows={rows} {inf}x{outf}: rel err {e}"
+    assert mod.ops.Workspace.get(torch.device("cuda"), 1, 128).status() == 0
+
+
+def test_fast_accum_on_the_golden_forwards(mod, golden):
+    """EXL3_FLAG_FAST_ACCUM against the forwards the reference itself produced (3INST / MCG
+    cases; MUL1 has no two-halves form and ignores the flag)."""
+    g = golden["forward"]
+    worst = 0.0
+    for i in range(int(g["n_cases"][0])):
+        k, mcg, mul1, inf, outf, rows, has_bias = (int(v) for v in g[f"c{i}_meta"])
+        layer = mod.EXL3Layer(f"c{i}", inf, outf, k, g[f"c{i}_trellis"],
+                              g[f"c{i}_suh"].view(np.float16), g[f"c{i}_svh"].view(np.float16),
+                              g[f"c{i}_bias"].view(np.float16) if has_bias else None,
+                              mcg=bool(mcg), mul1=bool(mul1))
+        m = mod.EXL3Linear(layer)
+        m.fast_accum = True
+        y = m(torch.from_numpy(g[f"c{i}_x"].view(np.float16)).cuda()).cpu().numpy()
+        e = rel_err(y, g[f"c{i}_y"].view(np.float16))
+        worst = max(worst, e)
+        assert e <= REL_TOL, f"case {i}: rel err {e}"
+    assert worst > 0.0          # the mode really is a different rounding
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096)] + FULL_SHAPES)
+@pytest.mark.parametrize("rows", [1, 16])
+def test_fast_accum_full_shapes(mod, oracle, shape, rows):
+    """The single-layer and sweep shapes at K=4 / 3INST in fast-accumulate mode."""
+    layer = _layer(mod, 4, shape[0], shape[1], seed=2300 + rows)
+    m = mod.EXL3Linear(layer)
+    m.fast_accum = True
+    x = np.random.default_rng(rows).standard_normal((rows, shape[0])).astype(np.float16)
+    y = m(torch.from_numpy(x).cuda()).cpu().numpy()
+    want = oracle.linear_forward(x, layer.trellis, 4, 0, layer.suh, layer.svh, None)
+    assert rel_err(y, want) <= REL_TOL
+
+
 def test_repeated_calls_are_deterministic_and_counters_rearm(mod, oracle):
     layer = _layer(mod, 5, 2048, 1024, seed=3)
     m = mod.EXL3Linear(layer)

@@ -46,6 +46,7 @@ def test_lane_windows_match_oracle(emul, oracle, k):
 
 def test_k4_fast_path_matches_oracle(emul, oracle):
     emul.emul_unpack_tile_k4_fast.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    emul.emul_unpack_tile_k4_halves.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     rng = np.random.default_rng(44)
     tiles = rng.integers(0, 65536, size=(200, 64), dtype=np.uint16)
     tiles[0] = 0xFFFF
@@ -54,6 +55,9 @@ def test_k4_fast_path_matches_oracle(emul, oracle):
     for packed in tiles:
         got = np.empty(256, dtype=np.uint16)
         emul.emul_unpack_tile_k4_fast(packed.ctypes.data, got.ctypes.data)
+        np.testing.assert_array_equal(got, oracle.unpack_trellis_tile(packed, 4))
+        got[:] = 0
+        emul.emul_unpack_tile_k4_halves(packed.ctypes.data, got.ctypes.data)
         np.testing.assert_array_equal(got, oracle.unpack_trellis_tile(packed, 4))
 
 

@@ -2,8 +2,9 @@
 that are only handed input and output buffers, decode loops where cudaMalloc is off limits).
 Its scratch is a fixed array inside the library, so the call takes no workspace.
 
-Called here through the C ABI and compared with exl3_gemv on the same inputs, two calls in a
-row with different shapes (the second call finds the array holding the first call's data).
+Called here through the C ABI and compared with exl3_gemv and with the CPU oracle on the same
+inputs, several calls in a row with different shapes (each finds the array holding the previous
+call's data); the status word of the built-in scratch must stay 0.
 The file name sorts last so that every other test has run before this one in a `-x` run.
 """
 
@@ -21,7 +22,7 @@ torch = pytest.importorskip("torch")
 REL_TOL = 1e-3
 
 
-def _call_pair(lib, ops, rows, inf, outf, k, cb, seed):
+def _call_pair(lib, ops, oracle, rows, inf, outf, k, cb, seed):
     dev = torch.device("cuda")
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
@@ -39,10 +40,12 @@ def _call_pair(lib, ops, rows, inf, outf, k, cb, seed):
                                got.data_ptr(), got.stride(0), 0, stream)
     assert rc == 0, lib.exl3_error_string(rc)
     torch.cuda.synchronize()
-    return got, want
+    ref = oracle.linear_forward(x.cpu().numpy(), tr.cpu().numpy().view(np.uint16), k, cb, suh.cpu().numpy(),
+                                svh.cpu().numpy(), bias.cpu().numpy())
+    return got, want, torch.from_numpy(ref.astype(np.float32))
 
 
-def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
+def test_noalloc_matches_workspace_entry_point_twice_in_a_row(oracle):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from ponyexl3_b200 import _lib, ops
@@ -52,10 +55,15 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
     # second call: other shape and K, fewer rows -> the array still holds the first call's words
     for rows, inf, outf, k, cb, seed in ((12, 2048, 1024, 4, 0, 1), (5, 4096, 512, 5, 1, 2),
                                          (1, 5120, 5120, 4, 0, 3)):
-        got, want = _call_pair(lib, ops, rows, inf, outf, k, cb, seed)
+        got, want, ref = _call_pair(lib, ops, oracle, rows, inf, outf, k, cb, seed)
         assert torch.isfinite(got.float()).all()
         err = float((got.float() - want.float()).norm() / want.float().norm())
-        assert err <= REL_TOL, f"rows={rows}: rel err {err}"
+        assert err <= REL_TOL, f"rows={rows}: rel err {err} against exl3_gemv"
+        err = float((got.float().cpu() - ref).norm() / ref.norm())
+        assert err <= REL_TOL, f"rows={rows}: rel err {err} against the oracle"
+    status = ctypes.c_int(-1)
+    assert lib.exl3_gemv_noalloc_status(ctypes.byref(status), torch.cuda.current_stream().cuda_stream) == 0
+    assert status.value == 0
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch():
