@@ -142,6 +142,18 @@ template <> __device__ __forceinline__ void load4_any<float>(const float* p, flo
     v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
 }
 
+// Compile-time loop: f(integral_constant<int, 0>) ... f(integral_constant<int, N-1>).  The tile
+// loops of the GEMV are written with it because `#pragma unroll` left them rolled (a branch, a
+// compare and two address computations per tile on the pipe that bounds the kernel).
+template <int V> struct IntC { static constexpr int value = V; };
+template <int N, int I0 = 0, typename F> __device__ __forceinline__ void static_for(F&& f)
+{
+    if constexpr (I0 < N) {
+        f(IntC<I0>{});
+        static_for<N, I0 + 1>(f);
+    }
+}
+
 // CTA that streams item i when I items are dealt to G CTAs as [I*c/G, I*(c+1)/G).
 __device__ __forceinline__ int cta_of_item(int64_t i, int64_t I, int G)
 {
@@ -288,8 +300,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
     long long gt_dep = 0, gt_last_item = 0, ck_wait = 0, ck_loop = 0;
 #endif
     const int prev_word = (lane + 31) & 31;
-    // A literal 16: handing it in as a run-time value (so that the nibble shift becomes a wide
-    // multiply) was measured slower, twice — the multiplier pipe is as busy as the logic pipe.
+    // A literal 16 (the nibble shift becomes two shift-adds on the logic pipe): handing it in as a
+    // run-time value, so that it becomes one wide multiply, was measured slower three times.
     const uint32_t sixteen = 16u;
     const uint32_t xor_const = a.cb_xor;   // 0x3B603B60, kept opaque on purpose (see exl3_bits.cuh)
     LaneWords<K> lw;
@@ -399,23 +411,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
 #pragma unroll
             for (int q = 0; q < 4; q++) acc[t][m][q] = 0.f;
 
-    // Both tiles (columns 2*tnp, 2*tnp + 1 of the item) of tile row tk: decode, multiply.
-    auto tile_row = [&](const uint8_t* st, const uint8_t* xk, int tk) {
+    // Both tiles (columns 2*tnp, 2*tnp + 1 of the item) of tile row TK: decode, multiply.
+    auto tile_row = [&](const uint8_t* xk, const uint32_t* wst, auto tkc) {
+        constexpr int tk = decltype(tkc)::value;
         uint2 xb[NMMA][2];
 #pragma unroll
         for (int m = 0; m < NMMA; m++)
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                if (XFUSED) {
+                if (XFUSED)
                     xb[m][h] = *reinterpret_cast<const uint2*>(xk + 64 * tk + 32 * h);
-                } else {
-                    const int o = (tk & 1) ? xo[2 + h] : xo[h];
-                    xb[m][h] = *reinterpret_cast<const uint2*>(xk + (tk >> 1) * (L::kXBoxRows * 128) + m * 1024 + o);
-                }
+                else
+                    xb[m][h] = *reinterpret_cast<const uint2*>(xk + (tk >> 1) * (L::kXBoxRows * 128) + m * 1024 +
+                                                               xo[2 * (tk & 1) + h]);
             }
-        const uint32_t* wst = reinterpret_cast<const uint32_t*>(st + xbox) + 2 * tnp * L::kTileWords;
-#pragma unroll
-        for (int t = 0; t < 2; t++) {
+        static_for<2>([&](auto tc) {
+            constexpr int t = decltype(tc)::value;
             const uint32_t* tw = wst + (tk * 8 + t) * L::kTileWords;
             uint32_t cw[8];
             if (K == 4) {
@@ -438,7 +449,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
                 mma_16816(acc[t][m], a1, xb[m][0].x, xb[m][0].y);
                 mma_16816(acc[t][m], a2, xb[m][1].x, xb[m][1].y);
             }
-        }
+        });
     };
 
     // Ring position of the item this thread looks at next; items are visited in rising order.
@@ -489,8 +500,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
             if (!failed) {
                 const uint8_t* st = stage0 + (size_t)s * stage_bytes;
                 const uint8_t* xk = XFUSED ? xs + (uint32_t)slot * xkb_step + xlane : st;
-#pragma unroll
-                for (int tk = 0; tk < 8; tk++) tile_row(st, xk, tk);
+                const uint32_t* wst = reinterpret_cast<const uint32_t*>(st + xbox) + 2 * tnp * L::kTileWords;
+                static_for<8>([&](auto tkc) { tile_row(xk, wst, tkc); });
             }
             release_stage(cur_p, s);
 #ifdef EXL3_PROFILE
