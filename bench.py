@@ -281,19 +281,22 @@ def run_gpu(args):
     from ponyexl3_b200.parallel import all_gather_columns
 
     # N > 1: every layer's output row is completed on every rank.  Default: the GEMV epilogue
-    # stores its blocks into all ranks' rows over peer memory (exl3_gemv_peers) and a one-thread
-    # kernel waits for the arrivals; --nccl-gather uses an NCCL all-gather per layer instead.
+    # stores its blocks into all ranks' rows over peer memory (exl3_gemv_peers) and the NEXT layer's
+    # kernel waits for the arrivals (a one-thread wait kernel after the last layer of the step);
+    # --nccl-gather uses an NCCL all-gather per layer instead.
     peer = None
     if dist is not None and not args.nccl_gather:
         from ponyexl3_b200.parallel import PeerExchange
-        peer = PeerExchange(ROWS, max(s[1] for s in SHAPES), ring=PeerExchange.ring_for(len(layers)))
+        # one (row buffer, counter) pair per layer of the step: the step's result is the ring itself
+        peer = PeerExchange(ROWS, max(s[1] for s in SHAPES), ring=len(layers))
 
     def one_layer(L, x):
         if dist is None:
             ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=True, out=L.y, fast_accum=args.fast_accum)
         elif peer is not None:
+            # the wait for a layer's arrivals is folded into the next layer's kernel
             L.y_full = ops.gemv_peers(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, exchange=peer,
-                                      out_features_total=L.outf, col0=L.c0, pdl=True)
+                                      out_features_total=L.outf, col0=L.c0, pdl=True, defer_wait=True)
         else:
             # between NCCL kernels plain stream order is kept (no programmatic launch)
             ops.gemv(x, L.trellis, K_BITS, CB, L.suh, L.svh, None, pdl=False, out=L.y)
@@ -308,6 +311,8 @@ def run_gpu(args):
             peer.restart()
         for L in layers:
             one_layer(L, xs[L.inf])
+        if peer is not None:
+            peer.settle(pdl=True)          # the last layer's arrivals
 
     stream = torch.cuda.Stream(device=dev)
     # NCCL all-gathers are captured with the kernels; every rank captures the same sequence
@@ -378,32 +383,61 @@ def run_gpu(args):
         mods.append(m)
     h_in = {inf: torch.randn((ROWS, inf)).to(torch.float16).pin_memory() for inf in xs}
     d_in = {inf: torch.empty_like(xs[inf]) for inf in xs}
-    # the step's result: every layer's output row, side by side in one device buffer that goes
-    # back to pinned host memory in one copy at the end of the step
-    widths = [m.full_out if dist is not None else m.out_features for m in mods]
-    d_out = torch.empty((ROWS, sum(widths)), dtype=torch.float16, device=dev)
-    h_out = torch.empty((ROWS, sum(widths)), dtype=torch.float16).pin_memory()
-    offs = [0]
-    for wd in widths:
-        offs.append(offs[-1] + wd)
-    d_views = [d_out[:, a:b] for a, b in zip(offs[:-1], offs[1:])]
     h2d = sum(v.numel() * 2 for v in h_in.values())
-    d2h = h_out.numel() * 2
+    e2e_graph = None
+    if dist is None or peer is None:
+        # the step's result: every layer's output row, side by side in one device buffer that goes
+        # back to pinned host memory in one copy at the end of the step
+        widths = [m.full_out if dist is not None else m.out_features for m in mods]
+        d_out = torch.empty((ROWS, sum(widths)), dtype=torch.float16, device=dev)
+        h_out = torch.empty((ROWS, sum(widths)), dtype=torch.float16).pin_memory()
+        offs = [0]
+        for wd in widths:
+            offs.append(offs[-1] + wd)
+        d_views = [d_out[:, a:b] for a, b in zip(offs[:-1], offs[1:])]
 
-    def e2e_step():
-        for inf in h_in:
-            d_in[inf].copy_(h_in[inf], non_blocking=True)
-        if dist is None:
-            for m, dv in zip(mods, d_views):
-                m(d_in[m.in_features], out=dv)
-        else:
-            if peer is not None:
-                peer.restart()
-            for L, dv in zip(layers, d_views):
+        def e2e_step():
+            for inf in h_in:
+                d_in[inf].copy_(h_in[inf], non_blocking=True)
+            if dist is None:
+                for m, dv in zip(mods, d_views):
+                    m(d_in[m.in_features], out=dv)
+            else:
+                for L, dv in zip(layers, d_views):
+                    one_layer(L, d_in[L.inf])
+                    dv.copy_(L.y_full)
+            h_out.copy_(d_out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        e2e_api = "EXL3Linear.forward per layer, pinned host x and y"
+    else:
+        # N > 1 over peer memory: every layer's completed row lands in its own slot of the exchange
+        # ring, so the whole ring goes back to the host in one copy; H2D, the layers and D2H are
+        # one CUDA graph (one launch per step instead of ~150 host calls)
+        d_out = peer.buf[:peer.ring * peer.slot_elems * 2].view(torch.float16)
+        h_out = torch.empty(d_out.shape, dtype=torch.float16).pin_memory()
+
+        def e2e_body():
+            for inf in h_in:
+                d_in[inf].copy_(h_in[inf], non_blocking=True)
+            peer.restart()
+            for L in layers:
                 one_layer(L, d_in[L.inf])
-                dv.copy_(L.y_full)
-        h_out.copy_(d_out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            peer.settle(pdl=True)
+            h_out.copy_(d_out, non_blocking=True)
+
+        with torch.cuda.stream(stream):
+            e2e_body()
+            stream.synchronize()
+            e2e_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(e2e_graph, stream=stream):
+                e2e_body()
+
+        def e2e_step():
+            e2e_graph.replay()
+            stream.synchronize()
+        e2e_api = ("ops.gemv_peers per layer (output rows completed on every rank over peer memory), pinned "
+                   "host x and y, the step captured in one CUDA graph")
+    d2h = h_out.numel() * 2
 
     e2e_steps = max(3, min(args.steps, 20))
     for _ in range(2):
@@ -418,6 +452,38 @@ def run_gpu(args):
         t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
+
+    # ---- N > 1: is the gathered row right?  One 5120 -> 17408 layer whose FULL trellis every rank draws
+    # from the same seed: each rank runs its column shard through the exchange, rank 0 also runs the
+    # unsharded layer on its own GPU and compares the two rows (outside every timed region).
+    tp_check = None
+    if dist is not None:
+        cg = torch.Generator(device=dev)
+        cg.manual_seed(4242)
+        inf, outf = SHAPES[0]
+        full = torch.randint(-32768, 32767, (inf // 16, outf // 16, 16 * K_BITS), dtype=torch.int16, device=dev,
+                             generator=cg)
+        c_suh = (torch.randint(0, 2, (inf,), device=dev, generator=cg) * 2 - 1).to(torch.float16)
+        c_svh = (torch.randint(0, 2, (outf,), device=dev, generator=cg) * 2 - 1).to(torch.float16)
+        c_x = torch.randn((ROWS, inf), device=dev, generator=cg).to(torch.float16)
+        c0, c1 = shard_cols(outf, world, rank)
+        shard = full[:, c0 // 16:c1 // 16].contiguous()
+        with torch.cuda.stream(stream):
+            if peer is not None:
+                peer.restart()
+                got = ops.gemv_peers(c_x, shard, K_BITS, CB, c_suh, c_svh[c0:c1].contiguous(), None, exchange=peer,
+                                     out_features_total=outf, col0=c0, pdl=False).clone()
+            else:
+                yl = ops.gemv(c_x, shard, K_BITS, CB, c_suh, c_svh[c0:c1].contiguous(), None)
+                got = all_gather_columns(yl, outf)
+            want = ops.gemv(c_x, full, K_BITS, CB, c_suh, c_svh, None)
+            stream.synchronize()
+        rel = float((got.float() - want.float()).norm() / want.float().norm())
+        t = torch.tensor([rel], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)          # every rank holds a gathered row: the worst one counts
+        tp_check = {"max_rel": float(t.item()), "ok": bool(float(t.item()) <= 1e-3),
+                    "what": "5120x17408 layer, gathered row of every rank vs the unsharded layer on the same GPU"}
+        del full, shard
 
     # ---- CPU baseline (rank 0, N = 1 only) -----------------------------------------------------------
     cpu = None
@@ -474,15 +540,21 @@ def run_gpu(args):
             "cpu_baseline": cpu,
             "e2e": {"value": step_bytes_global / e2e_s / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": 1e3 * e2e_s, "api": "EXL3Linear.forward per layer, pinned host x and y"},
-            "gpu_launches": n_gemv * args.steps,  # one fused kernel per layer (rotation inside)
+                    "ms_per_step": 1e3 * e2e_s, "api": e2e_api},
+            # one fused kernel per layer (rotation inside); over peer memory one wait kernel per step
+            "gpu_launches": (n_gemv + (1 if peer is not None else 0)) * args.steps,
             "clocks": clocks,
             "kernel_status": status,
         }
+        if tp_check is not None:
+            line["tp_check"] = tp_check
         emit(line)
     if dist is not None:
         graph = None          # the captured NCCL kernels go before the communicator does
+        e2e_graph = None
         finish_ranks(dist)
+        if tp_check is not None and not tp_check["ok"]:
+            raise SystemExit(f"tensor-parallel result differs from the unsharded layer: {tp_check}")
 
 
 def run_decode(args):

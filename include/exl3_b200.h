@@ -263,6 +263,20 @@ EXL3_API int exl3_gemv_peers(const void* x, int x_dtype, int rows, int64_t x_row
                              const uint64_t* y_peers, const uint64_t* counter_peers, int n_peers,
                              int64_t full_row_stride, int64_t col0, void* workspace, size_t workspace_bytes,
                              unsigned flags, exl3_stream_t stream);
+/* exl3_gemv_peers that FIRST waits for its own input: x is a row that the previous exchange
+ * completes on this rank, and instead of a separate exl3_peer_wait launch the kernel itself waits
+ * (bounded, same status value 16) until *wait_counter has grown by wait_target, then takes the
+ * arrivals off again; one kernel boundary per layer less.  Only the kernel that reads x can do
+ * that: when the call needs the separate rotation kernel (more rows than the fused rotation takes)
+ * the function launches nothing and returns EXL3_E_UNSUPPORTED — run exl3_peer_wait and
+ * exl3_gemv_peers instead.  No counterpart in the reference (single device). */
+EXL3_API int exl3_gemv_peers_after(const void* x, int x_dtype, int rows, int64_t x_row_stride,
+                                   const uint16_t* trellis, int64_t t_in, int64_t t_out, int k, int cb,
+                                   const uint16_t* suh, const uint16_t* svh, const uint16_t* bias,
+                                   const uint64_t* y_peers, const uint64_t* counter_peers, int n_peers,
+                                   int64_t full_row_stride, int64_t col0, uint32_t* wait_counter,
+                                   uint32_t wait_target, void* workspace, size_t workspace_bytes,
+                                   unsigned flags, exl3_stream_t stream);
 EXL3_API int exl3_peer_allgather(const uint16_t* src, int rows, int64_t cols, int64_t src_row_stride,
                                  const uint64_t* dst_peers, const uint64_t* counter_peers, int n_peers,
                                  int64_t dst_row_stride, int64_t col0, unsigned flags, exl3_stream_t stream);

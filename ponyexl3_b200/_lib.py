@@ -20,6 +20,7 @@ FLAG_PDL = 1
 FLAG_FAST_ACCUM = 2
 
 E_CUDA = -9
+E_UNSUPPORTED = -11
 _VALUE_ERRORS = {-1, -2, -3, -4, -5, -6, -7, -8, -10, -11}
 
 _PROTOTYPES = {
@@ -64,6 +65,9 @@ _PROTOTYPES = {
     "exl3_gemv_peers": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
                                 c_void_p, c_size_t, c_uint, c_void_p]),
+    "exl3_gemv_peers_after": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
+                                      c_void_p, c_uint, c_void_p, c_size_t, c_uint, c_void_p]),
     "exl3_peer_allgather": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64,
                                     c_int64, c_uint, c_void_p]),
     "exl3_peer_wait": (c_int, [c_void_p, c_uint, c_void_p, c_uint, c_void_p]),

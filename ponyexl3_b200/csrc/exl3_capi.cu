@@ -224,6 +224,8 @@ struct PeerOut {
     int64_t col0 = 0;
     const uint64_t* y = nullptr;      // host arrays of device pointers
     const uint64_t* ctr = nullptr;
+    uint32_t* wait_ctr = nullptr;     // the input row is complete after wait_target arrivals here
+    uint32_t wait_target = 0;
 };
 
 static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_stride, const uint16_t* trellis,
@@ -257,6 +259,9 @@ static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_strid
     cudaStream_t s = (cudaStream_t)stream;
 
     const bool x_fused = gemv_x_is_fused(rows, (int)t_in, t_out / 8, false, part_bytes);
+    // only the kernel that reads x can wait for it: with the separate rotation kernel the caller
+    // has to run exl3_peer_wait first
+    if (peer.wait_ctr && !x_fused) return EXL3_E_UNSUPPORTED;
     if (!x_fused) {
         rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
                              nullptr, reinterpret_cast<__half*>(xh), nullptr, nullptr, nullptr, pdl,
@@ -294,6 +299,9 @@ static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_strid
     a.n_peer = peer.n;
     a.y_col0 = peer.col0;
     a.done_ctr = reinterpret_cast<unsigned*>(ws + kWsDoneCtr);
+    a.wait_ctr = reinterpret_cast<unsigned*>(peer.wait_ctr);
+    a.wait_target = peer.wait_target;
+    a.pass_ctr = reinterpret_cast<unsigned*>(ws + kWsPassCtr);
     for (int p = 0; p < peer.n; p++) {
         a.y_peer[p] = reinterpret_cast<__half*>(peer.y[p]);
         a.ctr_peer[p] = reinterpret_cast<unsigned*>(peer.ctr[p]);
@@ -329,6 +337,32 @@ int exl3_gemv_peers(const void* x, int x_dtype, int rows, int64_t x_row_stride, 
     peer.y = y_peers;
     peer.ctr = counter_peers;
     // the local y of the plain entry point is unused; hand in rank 0's buffer for the checks
+    return gemv_common(x, x_dtype, rows, x_row_stride, trellis, t_in, t_out, k, cb, suh, svh, bias,
+                       reinterpret_cast<uint16_t*>(y_peers[0]), full_row_stride, workspace, workspace_bytes,
+                       flags, stream, peer);
+}
+
+int exl3_gemv_peers_after(const void* x, int x_dtype, int rows, int64_t x_row_stride, const uint16_t* trellis,
+                          int64_t t_in, int64_t t_out, int k, int cb, const uint16_t* suh, const uint16_t* svh,
+                          const uint16_t* bias, const uint64_t* y_peers, const uint64_t* counter_peers, int n_peers,
+                          int64_t full_row_stride, int64_t col0, uint32_t* wait_counter, uint32_t wait_target,
+                          void* workspace, size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+{
+    if (!y_peers || !counter_peers || !wait_counter) return EXL3_E_NULL;
+    if (n_peers < 1 || n_peers > kMaxPeers || wait_target == 0) return EXL3_E_RANGE;
+    if (col0 < 0 || col0 % 128 || col0 + 16 * t_out > full_row_stride) return EXL3_E_SHAPE;
+    if (reinterpret_cast<uintptr_t>(wait_counter) % 4) return EXL3_E_ALIGN;
+    for (int p = 0; p < n_peers; p++) {
+        if (!y_peers[p] || !counter_peers[p]) return EXL3_E_NULL;
+        if (y_peers[p] % 8 || counter_peers[p] % 4) return EXL3_E_ALIGN;
+    }
+    PeerOut peer;
+    peer.n = n_peers;
+    peer.col0 = col0;
+    peer.y = y_peers;
+    peer.ctr = counter_peers;
+    peer.wait_ctr = wait_counter;
+    peer.wait_target = wait_target;
     return gemv_common(x, x_dtype, rows, x_row_stride, trellis, t_in, t_out, k, cb, suh, svh, bias,
                        reinterpret_cast<uint16_t*>(y_peers[0]), full_row_stride, workspace, workspace_bytes,
                        flags, stream, peer);

@@ -51,7 +51,7 @@ static double plan_cost(int64_t ncb, int nkb, int g)
 
 // The items (column blocks x k-blocks) are dealt out evenly to `grid` virtual CTAs (two per SM:
 // the halves of the real CTA), fewer when the layer has fewer items or the caller's partial-sum
-// area holds fewer.  Among the counts down to three quarters of the largest one the cheapest by
+// area holds fewer.  Among the counts down to half of the largest one the cheapest by
 // plan_cost is taken: a count that lets ranges end on block boundaries (136 column blocks on 272
 // of 296 halves) saves more by avoiding second segments than it loses in idle SMs.  The choice
 // is remembered per shape.
@@ -74,7 +74,7 @@ GemvPlan gemv_plan(int64_t ncb, int nkb, int rows, bool table, size_t partial_by
             if (m.ncb == ncb && m.nkb == nkb && m.gmax == p.grid) best = m.best;
         if (!best) {
             double best_cost = 0;
-            for (int g = p.grid; g >= p.grid - p.grid / 4; g--) {
+            for (int g = p.grid; g >= p.grid - p.grid / 2; g--) {
                 const double cst = plan_cost(ncb, nkb, g);
                 if (!best || cst < best_cost - 1e-9) { best = g; best_cost = cst; }
             }

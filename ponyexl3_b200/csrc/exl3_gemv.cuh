@@ -375,6 +375,27 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
 #ifdef EXL3_PROFILE
         gt_dep = global_ns();
 #endif
+        // x may be a row that the other GPUs are still completing over peer memory: wait (bounded)
+        // until the expected number of ranks have announced their blocks on this rank's counter.
+        // The virtual CTA that is last to get past re-arms the counter by taking the arrivals off
+        // again, so an arrival that belongs to a later exchange is kept.
+        if (a.wait_ctr) {
+            if (tidh == 0) {
+                bool ok = false;
+                for (unsigned i = 0; i < kPeerPolls && !ok; i++) {
+                    unsigned v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.wait_ctr) : "memory");
+                    ok = v >= a.wait_target;
+                    if (!ok) __nanosleep(200);
+                }
+                if (!ok) atomicOr(a.status, ST_PEER_TIMEOUT);
+                const unsigned passed = atomicInc(a.pass_ctr, (unsigned)(G - 1));
+                if (ok && passed == (unsigned)(G - 1))
+                    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(a.wait_ctr), "r"(0u - a.wait_target)
+                                 : "memory");
+            }
+            named_bar_sync(hbar, kHalfThreads);
+        }
         for (int task = wl; task < ntask; task += 2 * kHalfWarps) {
             if (task != wl || a.blocks) {
                 make_task(task, t0);

@@ -47,6 +47,8 @@ constexpr int kMaxDevices = 64;
 //                 area only shrinks the grid)
 constexpr size_t kWsStatus = 0;
 constexpr size_t kWsDoneCtr = 64;   // finished-block counter of a launch with peer outputs (inside the status area)
+constexpr size_t kWsPassCtr = 68;   // virtual CTAs that got past the wait for a peer-completed input
+constexpr unsigned kPeerPolls = 1u << 22;      // x ~250 ns sleep: about a second
 constexpr size_t kWsSplitCtr = 256;
 constexpr int kGemvMaxGrid = 512;
 constexpr size_t kWsScratch = kWsSplitCtr + 4 * (size_t)kGemvMaxGrid;
@@ -119,6 +121,11 @@ struct GemvArgs {
     __half* y_peer[8];         // full-width (rows, y_row_stride) buffers of all ranks, this one included
     unsigned* ctr_peer[8];     // arrival counters of all ranks (one increment per rank and launch)
     unsigned* done_ctr;        // local: finished blocks of this launch (the last one announces the rank)
+    // input completed by the other ranks (fused rotation only): wait for wait_target arrivals on
+    // wait_ctr before x is read; pass_ctr counts the virtual CTAs that got past (the last re-arms)
+    unsigned* wait_ctr;        // NULL: x is ready when the previous kernel of the stream has ended
+    unsigned wait_target;
+    unsigned* pass_ctr;
 };
 constexpr int kMaxPeers = 8;
 

@@ -18,8 +18,6 @@
 
 namespace exl3 {
 
-constexpr unsigned kPeerPolls = 1u << 22;      // x ~250 ns sleep: about a second
-
 __global__ void peer_wait_kernel(unsigned* counter, unsigned target, int* status)
 {
     griddep_launch_dependents();

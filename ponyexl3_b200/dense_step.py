@@ -256,9 +256,12 @@ class SyntheticDenseDecoder:
         pdl = self.pdl_glue
 
         def gather(t, spans, total):
+            # the gathered row is read by the GEMV that follows: its kernel waits for the arrivals
+            # itself, no wait launch in between
             if peer is None:
                 return self._gather(t, spans)
-            return ops.peer_allgather(t, exchange=peer, cols_total=total, col0=spans[self.rank][0], pdl=pdl)
+            return ops.peer_allgather(t, exchange=peer, cols_total=total, col0=spans[self.rank][0], pdl=pdl,
+                                      defer_wait=True)
 
         def linear_gather(m, t, spans, total):
             if peer is None:

@@ -370,10 +370,14 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, pdl: bool = F
 # ---- output exchange over peer memory (exl3_peer.cu) -----------------------------------------
 
 def gemv_peers(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh, svh, bias, *, exchange,
-               out_features_total: int, col0: int, pdl: bool = False) -> torch.Tensor:
+               out_features_total: int, col0: int, pdl: bool = False, defer_wait: bool = False) -> torch.Tensor:
     """exl3_gemv whose output blocks land in every rank's full row (`exchange`: a
-    parallel.PeerExchange), followed by the wait for everybody's blocks.  Returns this rank's
-    complete (rows, out_features_total) row buffer."""
+    parallel.PeerExchange).  Returns this rank's (rows, out_features_total) row buffer.
+
+    The row is complete once every rank's blocks have arrived.  By default the wait for them is
+    launched right behind the GEMV.  With defer_wait=True it is left pending on the exchange: the
+    next gemv_peers call folds it into its own kernel (which then must read the pending row, or
+    at least run after it is complete), and `exchange.settle()` launches it for any other reader."""
     _need_cuda(x2d, "x")
     rows, in_features = x2d.shape
     t_in, t_out, _ = trellis.shape
@@ -383,29 +387,46 @@ def gemv_peers(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh, s
         x2d = x2d.contiguous()
     lib = _lib.load()
     ws = Workspace.get(x2d.device, rows, in_features)
+    pending = exchange.pending
     _, y_ptrs, c_ptrs, view, my_ctr = exchange.take(rows, out_features_total)
     ptr = lambda t: None if t is None else t.data_ptr()
-    _lib.check(lib.exl3_gemv_peers(
-        x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out, k, int(cb),
-        ptr(suh), ptr(svh), ptr(bias), y_ptrs, c_ptrs, exchange.world, out_features_total, int(col0),
-        ws.buf.data_ptr(), ws.nbytes, _lib.FLAG_PDL if pdl else 0, _stream(x2d.device)), "exl3_gemv_peers")
-    _lib.check(lib.exl3_peer_wait(my_ctr, exchange.world, ws.buf.data_ptr(), _flags(pdl),
-                                  _stream(x2d.device)), "exl3_peer_wait")
+    flags = _lib.FLAG_PDL if pdl else 0
+    rc = _lib.E_UNSUPPORTED
+    if pending is not None:
+        rc = lib.exl3_gemv_peers_after(
+            x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out, k, int(cb),
+            ptr(suh), ptr(svh), ptr(bias), y_ptrs, c_ptrs, exchange.world, out_features_total, int(col0),
+            pending, exchange.world, ws.buf.data_ptr(), ws.nbytes, flags, _stream(x2d.device))
+        if rc == 0:
+            exchange.pending = None
+    if rc == _lib.E_UNSUPPORTED:
+        exchange.settle(pdl=pdl)            # the rotation kernel reads x: the row has to be complete first
+        rc = lib.exl3_gemv_peers(
+            x2d.data_ptr(), _DTYPES[x2d.dtype], rows, x2d.stride(0), trellis.data_ptr(), t_in, t_out, k, int(cb),
+            ptr(suh), ptr(svh), ptr(bias), y_ptrs, c_ptrs, exchange.world, out_features_total, int(col0),
+            ws.buf.data_ptr(), ws.nbytes, flags, _stream(x2d.device))
+    _lib.check(rc, "exl3_gemv_peers")
+    exchange.pending = my_ctr
+    if not defer_wait:
+        exchange.settle(pdl=pdl)
     return view
 
 
-def peer_allgather(y_local: torch.Tensor, *, exchange, cols_total: int, col0: int, pdl: bool = False) -> torch.Tensor:
-    """(rows, local) slice -> this rank's complete (rows, cols_total) row, over peer memory."""
+def peer_allgather(y_local: torch.Tensor, *, exchange, cols_total: int, col0: int, pdl: bool = False,
+                   defer_wait: bool = False) -> torch.Tensor:
+    """(rows, local) slice -> this rank's complete (rows, cols_total) row, over peer memory.
+    defer_wait as in gemv_peers."""
     _need_cuda(y_local, "y_local")
     rows, cols = y_local.shape
     if y_local.stride(1) != 1:
         y_local = y_local.contiguous()
     lib = _lib.load()
-    ws = Workspace.get(y_local.device, 1, 128)
+    exchange.settle(pdl=pdl)
     _, y_ptrs, c_ptrs, view, my_ctr = exchange.take(rows, cols_total)
     _lib.check(lib.exl3_peer_allgather(y_local.data_ptr(), rows, cols, y_local.stride(0), y_ptrs, c_ptrs,
                                        exchange.world, cols_total, int(col0), _flags(pdl), _stream(y_local.device)),
                "exl3_peer_allgather")
-    _lib.check(lib.exl3_peer_wait(my_ctr, exchange.world, ws.buf.data_ptr(), _flags(pdl), _stream(y_local.device)),
-               "exl3_peer_wait")
+    exchange.pending = my_ctr
+    if not defer_wait:
+        exchange.settle(pdl=pdl)
     return view

@@ -219,6 +219,7 @@ class PeerExchange:
         dist.barrier(self.group)                      # everybody's counters are zero before first use
         self._u64 = ctypes.c_uint64 * self.world
         self._next = 0
+        self.pending = None       # counter address of an exchange whose arrivals nobody has waited for yet
 
     @staticmethod
     def ring_for(exchanges_per_replay: int) -> int:
@@ -231,6 +232,20 @@ class PeerExchange:
         while (exchanges_per_replay - 1) % r == 0:
             r += 1
         return r
+
+    def settle(self, pdl: bool = False) -> None:
+        """Launch the wait for a pending exchange (see ops.gemv_peers, defer_wait): after it, this
+        rank's row of that exchange is complete for every later kernel of the stream."""
+        if self.pending is None:
+            return
+        from . import _lib, ops
+
+        dev = torch.device("cuda", torch.cuda.current_device())
+        ws = ops.Workspace.get(dev, 1, 128)
+        _lib.check(_lib.load().exl3_peer_wait(self.pending, self.world, ws.buf.data_ptr(),
+                                              _lib.FLAG_PDL if pdl else 0,
+                                              torch.cuda.current_stream(dev).cuda_stream), "exl3_peer_wait")
+        self.pending = None
 
     def restart(self) -> None:
         """Start the rotation over: call at the top of a sequence that is captured in a CUDA graph
