@@ -30,6 +30,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 SHAPES = [(5120, 17408), (17408, 5120), (5120, 5120)]
+WORKLOAD = ("configs[1]: batch-1 GEMV, K=4, 3INST, shapes 5120x17408 + 17408x5120 + 5120x5120")
 K_BITS, CB, ROWS = 4, 0, 1
 CB_NAMES = {0: "3INST", 1: "MCG", 2: "MUL1"}
 METRIC = "exl3_gemv_packed_weight_bandwidth"
@@ -165,11 +166,10 @@ def run_reference(args):
         "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * t / steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": "configs[1]: batch-1 GEMV, K=4, 3INST, shapes 5120x17408 + "
-                               "17408x5120 + 5120x5120; one layer set per step",
-                   "rows": ROWS, "k": K_BITS, "codebook": "3INST"},
+        "config": {"workload": WORKLOAD, "rows": ROWS, "k": K_BITS, "codebook": "3INST",
+                   "step": "one layer set per step (GB/s does not depend on the step size)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{steps} x one layer set (3 layers, "
+                         "sample": f"{steps} x one layer set ({len(SHAPES)} layer(s), "
                                    f"{sum(packed_bytes(s) for s in SHAPES) / 1e6:.1f} MB packed)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -371,7 +371,7 @@ def run_gpu(args):
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    status = ops.Workspace.get(dev, ROWS, 17408).status()
+    status = ops.Workspace.get(dev, ROWS, max(s[0] for s in SHAPES)).status()
 
     # ---- end to end through the module API with host buffers --------------------------------
     mods = []
@@ -499,7 +499,7 @@ def run_gpu(args):
             pb, pt = cpu_pass(oracle, np, cl, cx, 25.0)
             b, dt, passes = b + pb, dt + pt, passes + 1
         cpu = {"value": b / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
-               "sample": f"{passes} passes over one layer set (3 layers, {b / passes / 1e6:.1f} MB packed "
+               "sample": f"{passes} passes over one layer set ({len(SHAPES)} layer(s), {b / passes / 1e6:.1f} MB packed "
                          f"each) through the C oracle with OpenMP, {dt:.1f} s"}
 
     if rank == 0:
@@ -512,8 +512,7 @@ def run_gpu(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {
-                "workload": "configs[1]: batch-1 GEMV, K=4, 3INST, shapes 5120x17408 + 17408x5120 + "
-                            "5120x5120",
+                "workload": WORKLOAD,
                 "rows": ROWS, "k": K_BITS, "codebook": "3INST", "ring_sets": args.ring,
                 "accumulate": "fast" if args.fast_accum else "exact",
                 "step_packed_bytes": step_bytes_global,
@@ -707,6 +706,122 @@ def run_decode(args):
         finish_ranks(dist)
 
 
+def run_gemm(args):
+    """The prefill configuration: M = 8192 tokens x 5120 -> 5120 at K = 4, 3INST, bf16 activations
+    N(0,1).  A step = one prefill call (input rotation kernel + tcgen05 GEMM) on the next layer of a
+    ring of distinct layers; x (84 MB), the rotated copy (84 MB) and y (84 MB) of one call are
+    already larger than the 126 MB L2.  value = 2*M*in*out FLOP / step time."""
+    import numpy as np
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback for the product path)")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    from ponyexl3_b200 import ops
+    from ponyexl3_b200.linear import EXL3Linear
+
+    M, inf, outf, k, cb = args.gemm_rows, 5120, 5120, 4, 0
+    g = torch.Generator(device=dev).manual_seed(3000)
+    ring = max(2, args.ring // 2)
+    trs = [torch.randint(-32768, 32767, (inf // 16, outf // 16, 16 * k), dtype=torch.int16, device=dev, generator=g)
+           for _ in range(ring)]
+    suh = (torch.randint(0, 2, (inf,), device=dev, generator=g) * 2 - 1).to(torch.float16)
+    svh = (torch.randint(0, 2, (outf,), device=dev, generator=g) * 2 - 1).to(torch.float16)
+    x = torch.randn((M, inf), device=dev, generator=g).to(torch.bfloat16)
+    y = torch.empty((M, outf), dtype=torch.float16, device=dev)
+    flops = 2.0 * M * inf * outf
+    stream = torch.cuda.Stream(device=dev)
+    stream.wait_stream(torch.cuda.current_stream(dev))
+
+    def timed(fn, steps, warm):
+        with torch.cuda.stream(stream):
+            for i in range(warm):
+                fn(i)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            stream.synchronize()
+            e0.record(stream)
+            for i in range(steps):
+                fn(i)
+            e1.record(stream)
+            stream.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(lambda i: ops.gemm(x, trs[i % ring], k, cb, suh, svh, None, out=y), args.steps, max(args.warmup, 3))
+    # keep the load up for the sampler
+    timed(lambda i: ops.gemm(x, trs[i % ring], k, cb, suh, svh, None, out=y), max(args.steps, int(250 / max(ms, 1e-3))), 0)
+    clocks = sampler.stop()
+    # the rotation kernel alone (same kernel, same x, fp16 output): its share of a call
+    rot_ms = timed(lambda i: ops.had_r_128(x, pre_scale=suh), args.steps, 3)
+    status = ops.Workspace.get(dev, 1, 128).status()
+
+    # end to end through the module with pinned host buffers
+    mod = EXL3Linear.from_device_tensors(trellis=trs[0], k=k, cb=cb, suh=suh, svh=svh, key="bench")
+    h_x = x.cpu().pin_memory()
+    h_y = torch.empty((M, outf), dtype=torch.float16).pin_memory()
+    d_x = torch.empty_like(x)
+
+    def e2e_step():
+        d_x.copy_(h_x, non_blocking=True)
+        h_y.copy_(mod(d_x), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    n_e2e = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    e2e_s = (time.perf_counter() - t0) / n_e2e
+
+    cpu = None
+    if not args.no_cpu:
+        from oracle import exl3_oracle as oracle
+        oracle.lib()
+        cores = oracle.host_cores()
+        oracle.set_threads(cores)
+        rows_s = 256
+        xs_np = x[:rows_s].float().cpu().numpy().astype(np.float16)
+        tr_np = trs[0].cpu().numpy().view(np.uint16)
+        t0 = time.perf_counter()
+        n = 0
+        while time.perf_counter() - t0 < 10.0:
+            oracle.linear_forward(xs_np, tr_np, k, cb, suh.cpu().numpy(), svh.cpu().numpy())
+            n += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": 2.0 * rows_s * inf * outf * n / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+               "sample": f"{n} forwards of {rows_s} of the {M} rows (decode of the whole layer each time) through "
+                         f"the C oracle with OpenMP, {dt:.1f} s"}
+    line = {
+        "metric": "exl3_prefill_gemm_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"configs[2]: prefill GEMM, M={M} tokens x {inf}->{outf}, K={k}, 3INST, bf16 "
+                               f"activations", "rows": M, "k": k, "codebook": "3INST", "ring_layers": ring,
+                   "flops": flops, "l2": "x, its rotated copy and y of one call (3 x 84 MB) exceed the 126 MB L2; "
+                                         "weights rotate over a ring of layers",
+                   "operands": "fp16 x fp16 -> fp32 (decoded weights are exact in fp16; the reference rounds "
+                               "the rotated activations to fp16)"},
+        "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": 1657.8, "unit": "TFLOP/s",
+                     "frac": flops / (ms * 1e-3) / 1e12 / 1657.8, "traffic": None,
+                     "peak_kind": "of measured (burst bf16 GEMM); sustained 1408.3",
+                     "frac_of_sustained": flops / (ms * 1e-3) / 1e12 / 1408.3,
+                     "kernel": "exl3::gemm_kernel (tcgen05) + exl3::hadamard_kernel",
+                     "rotation_ms": rot_ms, "gemm_kernel_ms_est": ms - rot_ms,
+                     "gemm_kernel_tflops_est": flops / ((ms - rot_ms) * 1e-3) / 1e12,
+                     "note": "achieved = FLOPs of the call / time of the call (rotation kernel included); the "
+                             "rotation kernel timed alone on the same x gives the split"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": flops / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * inf * 2,
+                "d2h_bytes_per_step": M * outf * 2, "ms_per_step": 1e3 * e2e_s,
+                "api": "EXL3Linear.forward, pinned host x (bf16) and y"},
+        "gpu_launches": 2 * args.steps, "clocks": clocks, "kernel_status": status,
+    }
+    emit(line)
+
+
 def run_moe(args):
     """The MoE expert-layer configuration: stacked-expert SwitchGLU, 256 experts, top-8, hidden 2048, expert
     intermediate 512, K=4, router logits N(0,1) -> softmax top-8, for --tokens 1, 16 or 4096.
@@ -803,6 +918,50 @@ def run_moe(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     status = ops.Workspace.get(dev, 1, 128).status()
+
+    # end to end (1 GPU): tokens and routing come from pinned host memory, the expert outputs go back
+    e2e = None
+    if world == 1:
+        h_x, h_i = x.cpu().pin_memory(), inds.cpu().pin_memory()
+        h_y = torch.empty((T, kk, D), dtype=torch.float16).pin_memory()
+        d_x, d_i = torch.empty_like(x), torch.empty_like(inds)
+
+        def e2e_step():
+            d_x.copy_(h_x, non_blocking=True)
+            d_i.copy_(h_i, non_blocking=True)
+            h_y.copy_(switch(d_x.view(1, T, D), d_i.view(1, T, kk)).view(T, kk, D), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(2):
+            e2e_step()
+        n_e2e = max(3, min(args.steps, 20))
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            e2e_step()
+        e2e_s = (time.perf_counter() - t0) / n_e2e
+        e2e = {"ms_per_step": 1e3 * e2e_s, "h2d_bytes_per_step": h_x.numel() * 2 + h_i.numel() * h_i.element_size(),
+               "d2h_bytes_per_step": h_y.numel() * 2, "api": "EXL3SwitchGLU.__call__, pinned host x, indices and y"}
+
+    # CPU baseline: the oracle's SwitchGLU on a bounded sample of (token, slot) pairs
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import numpy as np
+        from oracle import exl3_oracle as oracle
+        oracle.lib()
+        cores = oracle.host_cores()
+        oracle.set_threads(cores)
+        wn = {n: (t.cpu().numpy().view(np.uint16) if t.dtype == torch.int16 else t.cpu().numpy()) for n, t in w.items()}
+        n_pairs = min(T * kk, 64)
+        toks = np.arange(n_pairs) // kk if T * kk <= 64 else np.arange(n_pairs) * (T // n_pairs)
+        slots = np.arange(n_pairs) % kk
+        xi = x.cpu().numpy()[toks]
+        ii = inds.cpu().numpy()[toks, slots][:, None]
+        t0 = time.perf_counter()
+        oracle.switch_glu(xi, ii, **wn, k=k, cb=0)
+        dt = time.perf_counter() - t0
+        cpu = {"pairs": int(n_pairs), "seconds": dt, "cores": cores, "kind": "port",
+               "sample": f"{n_pairs} (token, slot) pairs of the same call through the C oracle "
+                         f"(decode of each distinct expert once, then three forwards per pair), {dt:.1f} s"}
     if rank == 0:
         touched = int(torch.unique(inds).numel())
         packed = touched * 3 * D * H * k // 8
@@ -826,7 +985,18 @@ def run_moe(args):
                           "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / world / 1657.8, "traffic": None,
                           "peak_kind": "of measured (burst)"}),
             "cpu_baseline": None, "e2e": None, "clocks": clocks, "kernel_status": status,
+            "gpu_launches": 5 * args.steps if world == 1 else None,
         }
+        unit_work = packed if few else flops        # what `value` counts per step
+        scale = 1e9 if few else 1e12
+        if e2e is not None:
+            e2e.update(value=unit_work / (e2e["ms_per_step"] * 1e-3) / scale, unit=line["unit"])
+            line["e2e"] = e2e
+        if cpu is not None:
+            # the sample's share of the step's work, over its time
+            share = cpu["pairs"] / float(T * kk)
+            cpu.update(value=unit_work * share / cpu["seconds"] / scale, unit=line["unit"])
+            line["cpu_baseline"] = cpu
         emit(line)
     if dist is not None:
         graph = None
@@ -961,9 +1131,11 @@ def main():
     ap.add_argument("--sweep-cb", default="0,1,2")
     ap.add_argument("--sweep-iters", type=int, default=5)
     ap.add_argument("--sweep-out", default=None, help="write a markdown table of the sweep here")
-    ap.add_argument("--workload", choices=["gemv", "decode", "moe"], default="gemv",
-                    help="gemv = the headline batch-1 GEMV ring; decode = the 64-layer decode step; "
+    ap.add_argument("--workload", choices=["gemv", "single", "gemm", "decode", "moe"], default="gemv",
+                    help="gemv = the headline batch-1 GEMV ring; single = one 4096x4096 layer (ring of copies); "
+                         "gemm = the 8192-token prefill GEMM; decode = the 64-layer decode step; "
                          "moe = the 256-expert SwitchGLU layer")
+    ap.add_argument("--gemm-rows", type=int, default=8192, help="gemm workload: tokens per call")
     ap.add_argument("--tokens", type=int, default=1, help="moe workload: tokens per step (1, 16, 4096)")
     ap.add_argument("--rows", type=int, default=1, help="decode workload: new positions per step (1 or 16)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: transformer layers")
@@ -976,8 +1148,17 @@ def main():
     if args.profile_case:
         run_profile_case(args.profile_case)
         return
+    if args.workload == "single":
+        # the single-layer configuration: in = out = 4096, K = 4, 3INST, x [1, 4096]; 8 MiB of packed
+        # weights per layer, so the ring holds 32 distinct layers (268 MB) to stay out of the L2
+        global SHAPES, WORKLOAD
+        SHAPES = [(4096, 4096)]
+        WORKLOAD = "configs[0]: single layer, in=out=4096, K=4, 3INST, x [1,4096]"
+        args.ring = max(args.ring, 32)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "gemm":
+        run_gemm(args)
     elif args.workload == "decode":
         run_decode(args)
     elif args.workload == "moe":
