@@ -62,6 +62,14 @@ extern "C" {
                                    instead of rounding their sum to fp16 first.  Saves one
                                    instruction per weight; outputs move by < 2e-4 relative */
 
+#define EXL3_FLAG_GLU_SILU 4u   /* exl3_gemv, exl3_gemv_blocks, exl3_gemv_noalloc: every x row holds */
+#define EXL3_FLAG_GLU_GELU 8u   /* [gate (in) | up (in)] (x_row_stride >= 2*in) and the layer's input is
+                                   fp16(silu(gate) * up) / fp16(gelu_tanh(gate) * up), computed while x
+                                   is read: the down projection of a gated MLP or of a SwitchGLU takes
+                                   the gate|up output as it is, with no activation launch in between
+                                   (the reference folds the GLU into its down kernel the same way,
+                                   ponyexl3/mlx/exl3_moe.py:374-422; activations :62-75) */
+
 typedef void* exl3_stream_t;    /* cudaStream_t */
 
 EXL3_API int exl3_version(void);

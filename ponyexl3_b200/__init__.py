@@ -14,6 +14,7 @@ _LAZY = {
     "EXL3Linear": ".linear",
     "FusedEXL3Group": ".fused",
     "FusedEXL3Sibling": ".fused",
+    "EXL3MLPMonolith": ".mlp",
     "EXL3SwitchGLU": ".moe",
     "EXL3MoEBlock": ".moe",
     "EXL3Checkpoint": ".loader",

@@ -18,6 +18,8 @@ LIB_PATH = _PKG / "lib" / "libexl3b200.so"
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 FLAG_PDL = 1
 FLAG_FAST_ACCUM = 2
+FLAG_GLU_SILU = 4
+FLAG_GLU_GELU = 8
 
 E_CUDA = -9
 E_UNSUPPORTED = -11

@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256)
                     const __half* __restrict__ pre, const __half* __restrict__ post,
                     __half* __restrict__ out, const int32_t* __restrict__ row_src,
                     const int32_t* __restrict__ pre_row, const int32_t* __restrict__ post_row,
-                    int wait_dependency, int out_mode)
+                    int wait_dependency, int out_mode, int glu)
 {
     // Let the next kernel of the stream (the GEMV that consumes `out`) start streaming its
     // weights right away; it waits for this grid before it reads any activation.
@@ -120,6 +120,13 @@ __global__ void __launch_bounds__(256)
             cc[u] = b * 128 + lane * 4;
             const int64_t rs = row_src ? row_src[r] : r;
             load4<T>(x + rs * x_row_stride + cc[u], v[u]);
+            if (glu && ok) {
+                // the row holds [gate (n) | up (n)]: the input is fp16(act(gate) * up)
+                float up[4];
+                load4<T>(x + rs * x_row_stride + n + cc[u], up);
+#pragma unroll
+                for (int q = 0; q < 4; q++) v[u][q] = glu_value(v[u][q], up[q], glu);
+            }
             if (pre) load4<__half>(pre + (pre_row ? (int64_t)pre_row[r] * n : 0) + cc[u], sp[u]);
         }
 #pragma unroll
@@ -241,7 +248,7 @@ int launch_table(int cb, __half* table, cudaStream_t s)
 int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
                     const __half* pre, const __half* post, __half* out, const int32_t* row_src,
                     const int32_t* pre_row, const int32_t* post_row, bool pdl, int out_mode,
-                    cudaStream_t s)
+                    cudaStream_t s, int glu)
 {
     if (rows * (n >> 7) >= ((int64_t)1 << 31)) return EXL3_E_RANGE;   // the kernel counts blocks in 32 bits
     const int g = grid_for(rows * (n >> 7), 8);
@@ -260,16 +267,16 @@ int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t
     switch (x_dtype) {
         case EXL3_DT_F16:
             e = cudaLaunchKernelEx(&cfg, hadamard_kernel<__half>, (const __half*)x, rows, n,
-                                   x_row_stride, pre, post, out, row_src, pre_row, post_row, wait, out_mode);
+                                   x_row_stride, pre, post, out, row_src, pre_row, post_row, wait, out_mode, glu);
             break;
         case EXL3_DT_BF16:
             e = cudaLaunchKernelEx(&cfg, hadamard_kernel<__nv_bfloat16>, (const __nv_bfloat16*)x,
                                    rows, n, x_row_stride, pre, post, out, row_src, pre_row, post_row,
-                                   wait, out_mode);
+                                   wait, out_mode, glu);
             break;
         case EXL3_DT_F32:
             e = cudaLaunchKernelEx(&cfg, hadamard_kernel<float>, (const float*)x, rows, n,
-                                   x_row_stride, pre, post, out, row_src, pre_row, post_row, wait, out_mode);
+                                   x_row_stride, pre, post, out, row_src, pre_row, post_row, wait, out_mode, glu);
             break;
         default: return EXL3_E_DTYPE;
     }

@@ -94,6 +94,11 @@ static long long* next_prof_slot()
 }
 #endif
 
+static int glu_mode(unsigned flags)
+{
+    return (flags & EXL3_FLAG_GLU_GELU) ? GLU_GELU : (flags & EXL3_FLAG_GLU_SILU) ? GLU_SILU : GLU_NONE;
+}
+
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 }  // namespace exl3
@@ -240,7 +245,8 @@ static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_strid
     if (t_in > (1 << 24) || t_out > (1 << 24)) return EXL3_E_SHAPE;
     if (rows < 1 || rows > 16) return EXL3_E_ROWS;
     const int64_t in = 16 * t_in, out = 16 * t_out;
-    if (x_row_stride < in || y_row_stride < out) return EXL3_E_SHAPE;
+    const int glu = glu_mode(flags);
+    if (x_row_stride < (glu ? 2 * in : in) || y_row_stride < out) return EXL3_E_SHAPE;
     int rc = check_dtype_align(x, x_dtype, x_row_stride);
     if (rc) return rc;
     if (!aligned(trellis, 16) || !aligned(y, 8) || y_row_stride % 4) return EXL3_E_ALIGN;
@@ -265,11 +271,12 @@ static int gemv_common(const void* x, int x_dtype, int rows, int64_t x_row_strid
     if (!x_fused) {
         rc = launch_hadamard(x, x_dtype, rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
                              nullptr, reinterpret_cast<__half*>(xh), nullptr, nullptr, nullptr, pdl,
-                             fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s);
+                             fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s, glu);
         if (rc) return rc;
     }
 
     GemvArgs a = {};
+    a.x_glu = glu;
     a.trellis = reinterpret_cast<const uint32_t*>(trellis);
     a.xh = xh;
     a.svh = reinterpret_cast<const __half*>(svh);
@@ -383,7 +390,8 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
     if (rows < 1 || rows > 16 || xh_rows < rows || xh_rows > (1 << 24)) return EXL3_E_ROWS;
     if (n_blocks < 0 || n_blocks > (1 << 24)) return EXL3_E_SHAPE;
     const int64_t in = 16 * t_in;
-    if (x_row_stride < in) return EXL3_E_SHAPE;
+    const int glu = glu_mode(flags);
+    if (x_row_stride < (glu ? 2 * in : in)) return EXL3_E_SHAPE;
     int rc = check_dtype_align(x, x_dtype, x_row_stride);
     if (rc) return rc;
     if (!aligned(trellis, 16) || !aligned(y, 8) || y_row_stride % 4 || !aligned(blocks, 16))
@@ -408,10 +416,11 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
     if (!x_fused) {
         rc = launch_hadamard(x, x_dtype, xh_rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
                              nullptr, reinterpret_cast<__half*>(xh), row_src, suh_row, nullptr, pdl,
-                             fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s);
+                             fast ? HAD_OUT_PAIR_XX : HAD_OUT_PAIR_X0, s, glu);
         if (rc) return rc;
     }
     GemvArgs a = {};
+    a.x_glu = glu;
     a.trellis = reinterpret_cast<const uint32_t*>(trellis);
     a.xh = xh;
     a.svh = reinterpret_cast<const __half*>(svh);

@@ -84,6 +84,18 @@ __device__ __forceinline__ void had128_warp(float (&v)[4], int lane)
 
 #define EXL3_HAD_SCALE 0.08838834764831845f
 
+// ---- gated linear unit ------------------------------------------------------------------------
+
+// act(g) * u in fp32 (the caller rounds to fp16): mode 1 = SiLU, 2 = tanh-GELU, the two
+// activations of the reference's SwitchGLU (ponyexl3/mlx/exl3_moe.py:62-75).
+enum : int { GLU_NONE = 0, GLU_SILU = 1, GLU_GELU = 2 };
+__device__ __forceinline__ float glu_value(float g, float u, int mode)
+{
+    if (mode == GLU_GELU)
+        return 0.5f * g * (1.f + tanhf(0.797884560803f * (g + 0.044715f * g * g * g))) * u;
+    return g / (1.f + __expf(-g)) * u;
+}
+
 // ---- shared-memory barriers and bulk copies ------------------------------------------------
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)

@@ -341,12 +341,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
             if (a.suh && t.dst >= 0) load4_any<__half>(a.suh + t.soff, sc);
             else sc[0] = sc[1] = sc[2] = sc[3] = 1.f;
         };
+        auto load_at = [&](int64_t off, float (&v)[4]) {
+            if (a.x_dtype == EXL3_DT_F16) load4_any<__half>(reinterpret_cast<const __half*>(a.x) + off, v);
+            else if (a.x_dtype == EXL3_DT_BF16)
+                load4_any<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(a.x) + off, v);
+            else load4_any<float>(reinterpret_cast<const float*>(a.x) + off, v);
+        };
         auto load_x = [&](const Task& t, float (&v)[4]) {
             if (t.dst < 0) return;
-            if (a.x_dtype == EXL3_DT_F16) load4_any<__half>(reinterpret_cast<const __half*>(a.x) + t.xoff, v);
-            else if (a.x_dtype == EXL3_DT_BF16)
-                load4_any<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(a.x) + t.xoff, v);
-            else load4_any<float>(reinterpret_cast<const float*>(a.x) + t.xoff, v);
+            load_at(t.xoff, v);
+            if (a.x_glu) {
+                // the row holds [gate (in) | up (in)]: the input is fp16(act(gate) * up), the
+                // rounding being the one rotate_store applies to every input
+                float up[4];
+                load_at(t.xoff + (int64_t)a.t_in * 16, up);
+#pragma unroll
+                for (int q = 0; q < 4; q++) v[q] = glu_value(v[q], up[q], a.x_glu);
+            }
         };
         auto rotate_store = [&](const Task& t, float (&v)[4], const float (&sc)[4]) {
             if (t.dst < 0) return;

@@ -65,7 +65,7 @@ enum : int { HAD_OUT_F16 = 0, HAD_OUT_PAIR_X0 = 1, HAD_OUT_PAIR_XX = 2 };
 int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
                     const __half* pre, const __half* post, __half* out, const int32_t* row_src,
                     const int32_t* pre_row, const int32_t* post_row, bool pdl, int out_mode,
-                    cudaStream_t s);
+                    cudaStream_t s, int glu = 0);   // glu: x rows are [gate (n) | up (n)], see glu_value
 
 // One logical 128-column output block of a streamed GEMV: where its weights, activations,
 // output scales and results live.  NULL descriptor table = the identity mapping of a plain
@@ -99,6 +99,7 @@ struct GemvArgs {
     int64_t x_row_stride;
     int x_dtype;
     int x_fused;               // 1: rotate x in the kernel; 0: xh was written by the rotation kernel
+    int x_glu;                 // GLU_*: x rows are [gate (in) | up (in)] and the input is fp16(act(gate) * up)
     const int32_t* row_src;    // fused rotation of a block-table launch: x row of rotated row i (NULL: i)
     const int32_t* suh_row;    // ... and its row of the stacked suh matrix (NULL: row 0)
     // split column blocks: partial sums and arrival counters in the workspace

@@ -78,7 +78,7 @@ def _rand_signs(n, dev, gen) -> torch.Tensor:
 
 
 class _Layer:
-    __slots__ = ("qkv", "o", "gate_up", "down", "norm1", "norm2", "k_cache", "v_cache")
+    __slots__ = ("qkv", "o", "gate_up", "down", "mlp", "norm1", "norm2", "k_cache", "v_cache")
 
 
 class SyntheticDenseDecoder:
@@ -159,6 +159,11 @@ class SyntheticDenseDecoder:
             L.down = EXL3Linear.from_device_tensors(trellis=tr, k=k_dn, cb=cb,
                                                     suh=_rand_signs(cfg.intermediate, device, gen), svh=sv,
                                                     key=f"l{li}.down")
+            # one GPU: gate|up -> GLU -> down as two launches (the GLU rides the down kernel's load)
+            L.mlp = None
+            if W == 1:
+                from .mlp import EXL3MLPMonolith
+                L.mlp = EXL3MLPMonolith(L.gate_up, L.down)
             for m in (L.qkv, L.o, L.gate_up, L.down):
                 m.pdl = pdl and (W == 1 or self.peer is not None)   # between NCCL kernels: plain stream order
                 self.packed_local += m.packed_bytes
@@ -279,8 +284,12 @@ class SyntheticDenseDecoder:
             a = gather(ops.attn_decode(q, L.k_cache, L.v_cache, c.context, pdl=pdl), head_spans, q_all)
             o = linear_gather(L.o, a, self.hidden_spans, c.hidden)
             h = ops.add_rmsnorm(x, o, L.norm2, c.rms_eps, pdl=pdl)
-            act = gather(ops.swiglu(L.gate_up.forward_packed(h), pdl=pdl), self.inter_spans, c.intermediate)
-            delta = linear_gather(L.down, act, self.hidden_spans, c.hidden)
+            if L.mlp is not None and rows <= 16:
+                L.mlp.pdl = L.down.pdl
+                delta = L.mlp(h)
+            else:
+                act = gather(ops.swiglu(L.gate_up.forward_packed(h), pdl=pdl), self.inter_spans, c.intermediate)
+                delta = linear_gather(L.down, act, self.hidden_spans, c.hidden)
         h = ops.add_rmsnorm(x, delta, self.final_norm, c.rms_eps, pdl=pdl)
         return self.head(h)
 

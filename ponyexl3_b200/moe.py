@@ -70,8 +70,9 @@ class EXL3SwitchGLU(torch.nn.Module):
 
     # ---- decode: every (token, slot) pair is a one-row problem -------------------------------
     def _decode(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
-        """Five launches: tables, rotation + GEMV over (pair, gate|up) blocks, GLU, rotation +
-        GEMV over (pair, down) blocks.  No host round trip, so the call can be captured."""
+        """Three launches: tables, GEMV over (pair, gate|up) blocks, GEMV over (pair, down) blocks
+        with the GLU folded into its activation load (the reference's two-launch fused decode,
+        ponyexl3/mlx/exl3_moe.py:345-422).  No host round trip, so the call can be captured."""
         from . import _lib
         E, D, H = self.num_experts, self.input_dims, self.hidden_dims
         R, kk = indices.shape
@@ -98,14 +99,11 @@ class EXL3SwitchGLU(torch.nn.Module):
         ops.gemv_blocks(x2d, xh_rows=2 * n, row_src=row_src, suh=self._gu_suh, suh_row=suh_row,
                         trellis=self._gu_trellis, k=self.k, cb=self.cb, blocks=blocks_gu, rows=1,
                         svh=self._gu_svh, bias=None, y=ygu, pdl=self.pdl)
-        if self.activation == "silu":
-            h = ops.swiglu(ygu, pdl=self.pdl)
-        else:
-            h = glu(ygu[:, :H], ygu[:, H:], self.activation)
+        # the down launch reads [gate | up] as it is and applies the GLU while loading
         y = torch.empty((n, D), dtype=torch.float16, device=dev)
-        ops.gemv_blocks(h, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=sel,
+        ops.gemv_blocks(ygu, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=sel,
                         trellis=self._dn_trellis, k=self.k, cb=self.cb, blocks=blocks_dn, rows=1,
-                        svh=self._dn_svh, bias=None, y=y, pdl=self.pdl)
+                        svh=self._dn_svh, bias=None, y=y, pdl=self.pdl, glu=self.activation)
         return y.view(R, kk, D)
 
     # ---- prefill: pairs sorted by expert, tensor-core GEMM over an expert tile table ----------

@@ -179,15 +179,21 @@ def had_r_128(x: torch.Tensor, *, pre_scale: torch.Tensor | None = None,
     return out
 
 
+_GLU_FLAGS = {None: 0, "silu": _lib.FLAG_GLU_SILU, "gelu": _lib.FLAG_GLU_GELU}
+
+
 def gemv(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh: torch.Tensor | None,
          svh: torch.Tensor | None, bias: torch.Tensor | None, *, pdl: bool = False,
-         fast_accum: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
-    """The whole linear forward for 1..16 rows in two launches (rotation, streamed GEMV).
-    x2d (rows, in) fp16/bf16/fp32 -> (rows, out) fp16."""
+         fast_accum: bool = False, out: torch.Tensor | None = None, glu: str | None = None) -> torch.Tensor:
+    """The whole linear forward for 1..16 rows in one launch (two for many rows: rotation, then the
+    streamed GEMV).  x2d (rows, in) fp16/bf16/fp32 -> (rows, out) fp16.
+    glu = "silu" | "gelu": x2d is (rows, 2*in) = [gate | up] and the input is fp16(act(gate) * up)."""
     _need_cuda(x2d, "x")
     rows, in_features = x2d.shape
+    if glu is not None:
+        in_features //= 2
     t_in, t_out, _ = trellis.shape
-    if in_features != t_in * 16:
+    if in_features != t_in * 16 or (glu is not None and x2d.shape[1] != 2 * in_features):
         raise ValueError(f"x has {in_features} features, layer expects {t_in * 16}")
     if x2d.dtype not in _DTYPES:
         raise ValueError(f"unsupported dtype {x2d.dtype}")
@@ -201,7 +207,7 @@ def gemv(x2d: torch.Tensor, trellis: torch.Tensor, k: int, cb: int, suh: torch.T
         k, int(cb), None if suh is None else suh.data_ptr(),
         None if svh is None else svh.data_ptr(), None if bias is None else bias.data_ptr(),
         y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes,
-        (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0),
+        (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0) | _GLU_FLAGS[glu],
         _stream(x2d.device)), "exl3_gemv")
     return y
 
@@ -236,12 +242,13 @@ def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None
                 suh: torch.Tensor | None, suh_row: torch.Tensor | None, trellis: torch.Tensor, k: int,
                 cb: int, blocks: torch.Tensor, rows: int, svh: torch.Tensor | None,
                 bias: torch.Tensor | None, y: torch.Tensor, raw_out: bool = False, pdl: bool = False,
-                fast_accum: bool = False) -> torch.Tensor:
+                fast_accum: bool = False, glu: str | None = None) -> torch.Tensor:
     """Streamed GEMV over a block table (see exl3_gemv_blocks in the header).  `blocks` is an
-    int32 CUDA tensor (n_blocks, 4) = phys, xrow, sv_off, y_off; `y` is written in place."""
+    int32 CUDA tensor (n_blocks, 4) = phys, xrow, sv_off, y_off; `y` is written in place.
+    glu as in gemv: x2d rows are [gate | up]."""
     _need_cuda(x2d, "x")
     t_in, t_out_total, _ = trellis.shape
-    if x2d.shape[1] != t_in * 16:
+    if x2d.shape[1] != t_in * 16 * (2 if glu is not None else 1):
         raise ValueError(f"x has {x2d.shape[1]} features, layer expects {t_in * 16}")
     if blocks.dtype != torch.int32 or blocks.ndim != 2 or blocks.shape[1] != 4:
         raise ValueError("blocks must be an int32 tensor of shape (n_blocks, 4)")
@@ -256,7 +263,7 @@ def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None
         ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), blocks.data_ptr(),
         blocks.shape[0], rows, ptr(svh), ptr(bias), y.data_ptr(), y.stride(0) if y.ndim == 2 else 0,
         1 if raw_out else 0, ws.buf.data_ptr(), ws.nbytes,
-        (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0),
+        (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0) | _GLU_FLAGS[glu],
         _stream(x2d.device)), "exl3_gemv_blocks")
     return y
 

@@ -192,3 +192,46 @@ def test_config4_4096_tokens_sampled(cuda, oracle):
     slots = rng.integers(0, kk, size=256)
     want = oracle.switch_glu(x[toks], idx[toks, slots][:, None], **w, k=k, cb=0)[:, 0]
     assert rel_err(y[toks, slots], want) <= 2e-3
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+@pytest.mark.parametrize("rows", [1, 3, 8, 16])
+def test_glu_folded_into_the_down_projection(cuda, oracle, act, rows):
+    """EXL3_FLAG_GLU_*: the GEMV reads [gate | up] rows and applies the activation while loading —
+    same result as the oracle's GLU (fp16 h) followed by its linear forward, for the fused
+    rotation (few rows) and the rotation-kernel path (many rows)."""
+    from ponyexl3_b200 import ops
+
+    H, D, k, cb = 1024, 512, 4, 0
+    tr, suh, svh, _ = synthetic_layer(k, H, D, seed=700 + rows)
+    rng = np.random.default_rng(rows)
+    gu = (rng.standard_normal((rows, 2 * H)) * 1.5).astype(np.float16)
+    h = oracle.glu(gu[:, :H], gu[:, H:], act)
+    want = oracle.linear_forward(h, tr, k, cb, suh, svh, None)
+    t = lambda a: torch.from_numpy(a).cuda()
+    y = ops.gemv(t(gu), t(tr.view(np.int16)), k, cb, t(suh), t(svh), None, glu=act)
+    assert rel_err(y.cpu().numpy(), want) <= 1e-3
+    assert ops.Workspace.get(torch.device("cuda"), 1, 128).status() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 5, 16, 40])
+def test_mlp_monolith_matches_the_three_linears(cuda, oracle, rows):
+    """gate|up -> SiLU-GLU -> down as one module (the reference's EXL3MLPMonolith): equals the
+    oracle's chain of linear forwards with h rounded to fp16 in between."""
+    import ponyexl3_b200
+    from ponyexl3_b200.fused import FusedEXL3Group
+    from ponyexl3_b200.linear import EXL3Linear
+    from ponyexl3_b200.mlp import EXL3MLPMonolith
+
+    D, H, k = 512, 1024, 4
+    gate, up = _members(k, D, [H, H], seed=1300)
+    trd, suhd, svhd, _ = synthetic_layer(k, H, D, seed=1310)
+    down = ponyexl3_b200.EXL3Layer("down", H, D, k, trd, suhd, svhd, None)
+    mlp = EXL3MLPMonolith.from_fused_gate_up(FusedEXL3Group([gate, up]), EXL3Linear(down))
+    x = (np.random.default_rng(rows).standard_normal((rows, D)) * 0.05).astype(np.float16)
+    y = mlp(torch.from_numpy(x).cuda())
+    g = oracle.linear_forward(x, gate.trellis, k, 0, gate.suh, gate.svh, None)
+    u = oracle.linear_forward(x, up.trellis, k, 0, up.suh, up.svh, None)
+    want = oracle.linear_forward(oracle.glu(g, u, "silu"), trd, k, 0, suhd, svhd, None)
+    assert y.shape == (rows, D)
+    assert rel_err(y.cpu().numpy(), want) <= 2e-3
