@@ -21,6 +21,10 @@ extern "C" {
  * is the maximum; 0 always uses the separate rotation kernel). */
 EXL3_API void exl3_tune_gemv(int max_grid, int fuse_x_bytes);
 
+/* one_acc_rows: 128 (default) = an output tile of the prefill GEMM with at most 128 rows loads,
+ * multiplies and drains only its first accumulator; 0 = every tile uses both (for comparison). */
+EXL3_API void exl3_tune_gemm(int one_acc_rows);
+
 #ifdef __cplusplus
 }
 #endif

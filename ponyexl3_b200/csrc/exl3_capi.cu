@@ -565,4 +565,9 @@ void exl3_tune_gemv(int max_grid, int fuse_x_bytes)
     gemv_set_tuning(max_grid, fuse_x_bytes);
 }
 
+void exl3_tune_gemm(int one_acc_rows)
+{
+    gemm_set_tuning(one_acc_rows);
+}
+
 }  // extern "C"

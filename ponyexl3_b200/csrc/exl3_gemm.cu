@@ -4,6 +4,9 @@
 
 namespace exl3 {
 
+int g_gemm_one_acc_rows = 128;
+void gemm_set_tuning(int one_acc_rows) { g_gemm_one_acc_rows = one_acc_rows == 0 ? 0 : 128; }
+
 template <int K>
 int launch_gemm_k(const GemmArgs& a, int cb, const __half* xh, const uint32_t* trellis, cudaStream_t s);
 #define EXL3_DECL(K) \

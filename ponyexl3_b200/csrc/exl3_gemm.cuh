@@ -153,6 +153,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const GemmTile ti = gemm_tile(a, tile);
                 if (ti.m0 >= ti.m_end) continue;
                 const int m0 = ti.m0, tn0 = ti.tn0;
+                const bool two = ti.m_end - ti.m0 > a.one_acc_rows;   // tiles of up to 128 rows use one accumulator
                 for (int ks = 0; ks < nks; ks++) {
                     if (!first_pass && !mbar_wait(smem_u32(&empty[s]), parity ^ 1u)) {
                         atomicOr(a.status, ST_TC_TIMEOUT);
@@ -160,9 +161,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     }
                     uint8_t* st = stage0 + (size_t)s * L::kStageBytes;
                     const uint32_t bar = smem_u32(&a_full[s]);
-                    mbar_arrive_expect_tx(bar, 2 * kABytes + L::kWBytes);
+                    mbar_arrive_expect_tx(bar, (two ? 2 : 1) * kABytes + L::kWBytes);
                     tma_load_2d(smem_u32(st), &tm_x, ks * kStepK, m0, bar);
-                    tma_load_2d(smem_u32(st + kABytes), &tm_x, ks * kStepK, m0 + 128, bar);
+                    if (two) tma_load_2d(smem_u32(st + kABytes), &tm_x, ks * kStepK, m0 + 128, bar);
                     tma_load_3d(smem_u32(st + 2 * kABytes + kBBytes), &tm_w, 0, tn0, 4 * ks, bar);
                     if (++s == NS) { s = 0; parity ^= 1u; first_pass = false; }
                 }
@@ -176,9 +177,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             uint32_t parity = 0, tile_parity = 0;
             bool first_tile = true;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                bool two;
                 {
                     const GemmTile ti = gemm_tile(a, tile);
                     if (ti.m0 >= ti.m_end) continue;
+                    two = ti.m_end - ti.m0 > a.one_acc_rows;
                 }
                 if (!first_tile) {   // the epilogue of the previous tile must have drained D
                     if (!mbar_wait(smem_u32(tmem_empty), tile_parity ^ 1u)) {
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         const uint64_t db = smem_desc_sw128(sa + 2 * kABytes + kk * 32);
                         const uint32_t accum = (ks | kk) != 0 ? 1u : 0u;
                         tc_mma_f16(tmem_base, da0, db, idesc, accum);
-                        tc_mma_f16(tmem_base + kTileN, da1, db, idesc, accum);
+                        if (two) tc_mma_f16(tmem_base + kTileN, da1, db, idesc, accum);
                     }
                     tc_commit(smem_u32(&empty[s]));
                     if (++s == NS) { s = 0; parity ^= 1u; }
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const int col0 = ti.y_col + 128 * chalf, sv0 = ti.sv_off + 128 * chalf;
             if (128 * chalf < ti.ncols) {
 #pragma unroll 1
-                for (int acc = 0; acc < 2; acc++) {
+                for (int acc = 0; acc < (ti.m_end - m0 > a.one_acc_rows ? 2 : 1); acc++) {
                     const int row = m0 + 128 * acc + 32 * quarter + lane;
                     const uint32_t taddr =
                         tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(kTileN * acc + 128 * chalf);
@@ -338,6 +341,8 @@ done:
 
 // ---- host side ----------------------------------------------------------------------------------
 
+extern int g_gemm_one_acc_rows;   // exl3_gemm.cu: 128, or 0 from the benchmark hook (always two accumulators)
+
 template <int K, int CB>
 static int launch_gemm_t(GemmArgs a, const __half* xh, const uint32_t* trellis, cudaStream_t s)
 {
@@ -370,6 +375,7 @@ static int launch_gemm_t(GemmArgs a, const __half* xh, const uint32_t* trellis, 
     a.tiles_m = (a.m + kTileM - 1) / kTileM;
     a.tiles_n = (a.t_out * 16 + kTileN - 1) / kTileN;
     a.cb_xor = 0x3B603B60u;
+    a.one_acc_rows = g_gemm_one_acc_rows;
     const int grid = std::min(a.tile_tab ? a.n_tiles_tab : a.tiles_m * a.tiles_n, device_sm_count());
     gemm_kernel<K, CB><<<grid, kGemmThreads, L::kSmemBytes, s>>>(a, tm_x, tm_w);
     return check_launch();

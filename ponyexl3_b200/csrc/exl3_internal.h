@@ -144,7 +144,8 @@ struct GemvPlan {
     bool x_fused;
 };
 GemvPlan gemv_plan(int64_t ncb, int nkb, int rows, bool table, size_t partial_bytes);
-void gemv_set_tuning(int max_grid, int fuse_x_bytes);   // benchmark hook, see exl3_b200_tuning.h
+void gemv_set_tuning(int max_grid, int fuse_x_bytes);
+void gemm_set_tuning(int one_acc_rows);                      // benchmark hook, see exl3_b200_tuning.h   // benchmark hook, see exl3_b200_tuning.h
 
 // ---- prefill GEMM (exl3_gemm.cuh) ---------------------------------------------------------
 struct GemmArgs {
@@ -161,6 +162,7 @@ struct GemmArgs {
     int t_in, t_out;          // tiles
     int tiles_m, tiles_n;
     int stages;
+    int one_acc_rows;         // tiles with at most this many rows use only the first accumulator
     uint32_t cb_xor;
 };
 
