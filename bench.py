@@ -37,7 +37,7 @@ METRIC = "exl3_gemv_packed_weight_bandwidth"
 UNIT = "GB/s"
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum over packed weight bytes, from the ncu capture of
-# the K=4 batch-1 GEMV 5120 -> 17408 (profiles/gemv_k4_b1_5120x17408.md)
+# the K=4 batch-1 GEMV 5120 -> 17408
 DRAM_TRAFFIC_RATIO = 1.0027
 
 
@@ -867,7 +867,7 @@ def run_moe(args):
         if T <= 16:
             ep = EPSwitchGLU(local_sw, E)
             step = lambda: ep(x.view(1, T, D), inds.view(1, T, kk))
-            mode = f"ep{world}: tokens replicated, all-reduce of partial outputs"
+            mode = f"ep{world}: tokens replicated, pairs picked on the device, all-reduce of partial outputs, one CUDA graph"
         else:
             t0, t1 = T * rank // world, T * (rank + 1) // world
             xl, il = x[t0:t1].contiguous(), inds[t0:t1].contiguous()
@@ -892,9 +892,10 @@ def run_moe(args):
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
-        # one GPU: no host round trip anywhere, the call is captured.  Expert parallel: each rank
-        # picks its pairs with a host-visible count (nonzero / split sizes), so it runs eagerly.
-        if world == 1 and not args.no_graph:
+        # No host round trip anywhere on one GPU, nor for few tokens under expert parallelism (each
+        # rank's pairs are picked on the device): the call is captured, the all-reduce included.
+        # Many tokens under expert parallelism exchange rows with host-visible split sizes: eager.
+        if (world == 1 or T <= 16) and not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()

@@ -152,6 +152,18 @@ EXL3_API int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, 
                      const uint16_t* bias, uint16_t* y, int64_t y_row_stride, int raw_out,
                      void* workspace, size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
 
+/* exl3_gemv_blocks with the number of blocks in use read from the device: *n_blocks_dev
+ * (int32, written by an earlier kernel of the stream, clamped to 0..max_blocks) blocks of the
+ * table are computed; the launch is planned for max_blocks, so nothing about it depends on a
+ * value the host has not seen (expert-parallel SwitchGLU, exl3_moe_decode_tables_range). */
+EXL3_API int exl3_gemv_blocks_counted(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                             const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                             const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                             const int32_t* blocks, int64_t max_blocks, const int32_t* n_blocks_dev, int rows,
+                             const uint16_t* svh, const uint16_t* bias, uint16_t* y, int64_t y_row_stride,
+                             int raw_out, void* workspace, size_t workspace_bytes, unsigned flags,
+                             exl3_stream_t stream);
+
 /* Same contract for any number of rows (prefill): the packed tiles are decoded to fp16 in
  * shared memory and multiplied on the tensor cores (tcgen05.mma, fp32 accumulators in tensor
  * memory) against TMA-staged rotated activations; W is never materialised in global memory.
@@ -238,7 +250,9 @@ EXL3_API int exl3_rope_append(const uint16_t* qkv, int64_t qkv_row_stride, const
 
 /* Grouped-query attention of `rows` (1..16) new positions over caches that already hold them:
  * position r sees keys 0 .. ctx + r.  q (rows, q_heads, 128) -> out (rows, q_heads * 128).
- * (q_heads / kv_heads) * rows <= 128.  Workspace from exl3_attn_workspace_bytes, 16-byte aligned. */
+ * (q_heads / kv_heads) * rows <= 128.  Workspace from exl3_attn_workspace_bytes, 16-byte aligned;
+ * the size does not grow with total_keys (it is the bound over all context lengths), so one
+ * workspace sized once serves a whole generation. */
 EXL3_API size_t exl3_attn_workspace_bytes(int rows, int q_heads, int kv_heads, int64_t total_keys);
 EXL3_API int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache,
                               uint16_t* out, int rows, int q_heads, int kv_heads, int64_t cache_len, int ctx,
@@ -306,6 +320,21 @@ EXL3_API int exl3_moe_decode_tables(const void* indices, int index_bytes, int n_
                                     int num_experts, int64_t d, int64_t h, int32_t* blocks_gu,
                                     int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* blocks_dn,
                                     int32_t* suh_row_dn, unsigned flags, exl3_stream_t stream);
+
+/* Expert parallelism (the stacked tensors passed to the GEMV hold only experts expert_lo ..
+ * expert_hi-1 of num_experts; indices stay global): only the pairs routed to a held expert get
+ * blocks, packed to the front of both tables in pair order, and the numbers of blocks in use are
+ * left in counts[0] (gate/up) and counts[1] (down), a device int32[2], for
+ * exl3_gemv_blocks_counted.  Rows and output offsets keep the numbering of ALL pairs, so the
+ * output rows of pairs computed on another GPU are never written (the caller zero-fills them
+ * and sums the ranks' outputs).  n_pairs <= 2048.  Nothing comes back to the host: the whole
+ * call can be captured in a CUDA graph.  The reference has no multi-device path; the pair ->
+ * expert mapping is the one of ponyexl3/mlx/exl3_moe.py:634-683. */
+EXL3_API int exl3_moe_decode_tables_range(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                          int num_experts, int expert_lo, int expert_hi, int64_t d, int64_t h,
+                                          int32_t* blocks_gu, int32_t* row_src_gu, int32_t* suh_row_gu,
+                                          int32_t* blocks_dn, int32_t* suh_row_dn, int32_t* counts,
+                                          unsigned flags, exl3_stream_t stream);
 
 /* Prefill-class SwitchGLU tables, built on the device by one kernel (no host round trip): the
  * n_pairs (token, slot) pairs are grouped by expert (a counting sort; the order inside an expert

@@ -45,6 +45,10 @@ _PROTOTYPES = {
                                  c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_int,
                                  c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_size_t,
                                  c_uint, c_void_p]),
+    "exl3_gemv_blocks_counted": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
+                                         c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p,
+                                         c_size_t, c_uint, c_void_p]),
     "exl3_gemm_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "exl3_gemm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_size_t,
@@ -79,6 +83,9 @@ _PROTOTYPES = {
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
     "exl3_moe_decode_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
+    "exl3_moe_decode_tables_range": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64,
+                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_uint, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

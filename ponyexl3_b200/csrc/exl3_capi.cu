@@ -375,12 +375,13 @@ int exl3_gemv_peers_after(const void* x, int x_dtype, int rows, int64_t x_row_st
                        flags, stream, peer);
 }
 
-int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
-                     const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
-                     const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
-                     const int32_t* blocks, int64_t n_blocks, int rows, const uint16_t* svh,
-                     const uint16_t* bias, uint16_t* y, int64_t y_row_stride, int raw_out,
-                     void* workspace, size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+static int gemv_blocks_impl(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                            const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                            const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                            const int32_t* blocks, int64_t n_blocks, const int32_t* n_blocks_dev, int rows,
+                            const uint16_t* svh, const uint16_t* bias, uint16_t* y, int64_t y_row_stride,
+                            int raw_out, void* workspace, size_t workspace_bytes, unsigned flags,
+                            exl3_stream_t stream)
 {
     if (!x || !trellis || !y || !blocks) return EXL3_E_NULL;
     if (k < 1 || k > 8) return EXL3_E_K;
@@ -432,6 +433,7 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
     a.t_in = (int)t_in;
     a.t_out_total = (int)t_out_total;
     a.ncb = (int)n_blocks;
+    a.ncb_dev = n_blocks_dev;
     a.rows = rows;
     a.x_rows_total = (int)xh_rows;
     a.raw_out = raw_out ? 1 : 0;
@@ -448,6 +450,33 @@ int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t x
     a.split_ctr = reinterpret_cast<unsigned*>(ws + kWsSplitCtr);
     a.done_ctr = reinterpret_cast<unsigned*>(ws + kWsDoneCtr);
     return launch_gemv(a, k, cb, pdl, s);
+}
+
+int exl3_gemv_blocks(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                     const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                     const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                     const int32_t* blocks, int64_t n_blocks, int rows, const uint16_t* svh,
+                     const uint16_t* bias, uint16_t* y, int64_t y_row_stride, int raw_out,
+                     void* workspace, size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+{
+    return gemv_blocks_impl(x, x_dtype, x_row_stride, xh_rows, row_src, suh, suh_row, trellis, t_in, t_out_total,
+                            k, cb, blocks, n_blocks, nullptr, rows, svh, bias, y, y_row_stride, raw_out,
+                            workspace, workspace_bytes, flags, stream);
+}
+
+int exl3_gemv_blocks_counted(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                             const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                             const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                             const int32_t* blocks, int64_t max_blocks, const int32_t* n_blocks_dev, int rows,
+                             const uint16_t* svh, const uint16_t* bias, uint16_t* y, int64_t y_row_stride,
+                             int raw_out, void* workspace, size_t workspace_bytes, unsigned flags,
+                             exl3_stream_t stream)
+{
+    if (!n_blocks_dev) return EXL3_E_NULL;
+    if (reinterpret_cast<uintptr_t>(n_blocks_dev) % 4) return EXL3_E_ALIGN;
+    return gemv_blocks_impl(x, x_dtype, x_row_stride, xh_rows, row_src, suh, suh_row, trellis, t_in, t_out_total,
+                            k, cb, blocks, max_blocks, n_blocks_dev, rows, svh, bias, y, y_row_stride, raw_out,
+                            workspace, workspace_bytes, flags, stream);
 }
 
 size_t exl3_gemm_workspace_bytes(int64_t rows, int64_t in)

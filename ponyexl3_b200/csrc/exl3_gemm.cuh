@@ -238,28 +238,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 uint8_t* st = stage0 + (size_t)s * L::kStageBytes;
                 uint8_t* bt = st + 2 * kABytes;
                 const uint32_t* wt = reinterpret_cast<const uint32_t*>(bt + kBBytes);
+                // All packed words of the warp's eight tiles are fetched before the first store: the
+                // stores into the B tile could alias the packed words as far as the compiler knows,
+                // so loads written after them would wait for them, tile after tile.
+                uint32_t pw[8][3];
 #pragma unroll
-                for (int tk = 0; tk < 4; tk++)
-#pragma unroll
-                    for (int t = 0; t < 2; t++) {
-                        const int tn = 2 * dw + t;
-                        const uint32_t* tw = wt + (tk * 16 + tn) * L::kTileWords;
-                        uint32_t cw[8];
-                        if (K == 4) {
-                            lane_codewords_k4(tw[lane], tw[prev_word], cw);
-                        } else {
-                            const uint32_t wa = tw[lw.i0], wb = tw[lw.i1];
-                            const uint32_t wc = LaneWords<K>::kThree ? tw[lw.i2] : 0u;
-                            lane_codewords<K>(wa, wb, wc, lw.sh, cw);
-                        }
-                        // B[n][k] K-major, 128B swizzle: n = 16 tn + g (+8), k = 16 tk + 2q (+8)
-                        uint8_t* row = bt + (2 * tn) * 1024 + g * 128 + 4 * q;
-                        const int c0 = ((2 * tk) ^ g) << 4, c1 = ((2 * tk + 1) ^ g) << 4;
-                        *reinterpret_cast<uint32_t*>(row + c0) = decode_pair_rt<CB>(cw[0], cw[1], xc);
-                        *reinterpret_cast<uint32_t*>(row + 1024 + c0) = decode_pair_rt<CB>(cw[4], cw[5], xc);
-                        *reinterpret_cast<uint32_t*>(row + c1) = decode_pair_rt<CB>(cw[2], cw[3], xc);
-                        *reinterpret_cast<uint32_t*>(row + 1024 + c1) = decode_pair_rt<CB>(cw[6], cw[7], xc);
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t* tw = wt + ((i >> 1) * 16 + 2 * dw + (i & 1)) * L::kTileWords;
+                    if (K == 4) {
+                        pw[i][0] = tw[lane];
+                        pw[i][1] = tw[prev_word];
+                        pw[i][2] = 0u;
+                    } else {
+                        pw[i][0] = tw[lw.i0];
+                        pw[i][1] = tw[lw.i1];
+                        pw[i][2] = LaneWords<K>::kThree ? tw[lw.i2] : 0u;
                     }
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int tk = i >> 1, tn = 2 * dw + (i & 1);
+                    uint32_t cw[8];
+                    if (K == 4) lane_codewords_k4(pw[i][0], pw[i][1], cw);
+                    else lane_codewords<K>(pw[i][0], pw[i][1], pw[i][2], lw.sh, cw);
+                    // B[n][k] K-major, 128B swizzle: n = 16 tn + g (+8), k = 16 tk + 2q (+8)
+                    uint8_t* row = bt + (2 * tn) * 1024 + g * 128 + 4 * q;
+                    const int c0 = ((2 * tk) ^ g) << 4, c1 = ((2 * tk + 1) ^ g) << 4;
+                    *reinterpret_cast<uint32_t*>(row + c0) = decode_pair_rt<CB>(cw[0], cw[1], xc);
+                    *reinterpret_cast<uint32_t*>(row + 1024 + c0) = decode_pair_rt<CB>(cw[4], cw[5], xc);
+                    *reinterpret_cast<uint32_t*>(row + c1) = decode_pair_rt<CB>(cw[2], cw[3], xc);
+                    *reinterpret_cast<uint32_t*>(row + 1024 + c1) = decode_pair_rt<CB>(cw[6], cw[7], xc);
+                }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&b_full[s]));
@@ -347,10 +356,11 @@ template <int K, int CB>
 static int launch_gemm_t(GemmArgs a, const __half* xh, const uint32_t* trellis, cudaStream_t s)
 {
     using L = GemmLayout<K>;
-    static bool attr_set[16] = {};
+    static bool attr_set[kMaxDevices] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 16 && !attr_set[dev]) {
+    if (dev < 0 || dev >= kMaxDevices) return EXL3_E_UNSUPPORTED;
+    if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_kernel<K, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              L::kSmemBytes);
         if (e != cudaSuccess) return note_cuda(e);

@@ -183,9 +183,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
     // The CTA is two independent halves of 16 warps; each is one "virtual CTA" of the partition.
     const int half = warp >> 4, wl = warp & 15, tidh = tid & (kHalfThreads - 1);
     const int hbar = 1 + half;                         // the half's named barrier
-    const int G = a.grid_virtual, c = 2 * (int)blockIdx.x + half;
+    const int c = 2 * (int)blockIdx.x + half;
     const int nkb = a.t_in >> 3;
-    const int64_t I = (int64_t)a.ncb * nkb;
+    // The number of column blocks may be a count that an earlier kernel of the stream has left on
+    // the device (a table of which only the first entries are in use): every thread reads the same
+    // word, so the partition below is the same in every CTA.  The plan was made for a.ncb blocks.
+    int ncb = a.ncb;
+    if (a.ncb_dev) {
+        griddep_wait();
+        const int v = *a.ncb_dev;
+        ncb = v < 0 ? 0 : (v < a.ncb ? v : a.ncb);
+    }
+    const int64_t I = (int64_t)ncb * nkb;
+    // Every virtual CTA of the partition holds at least one item (the hand-over of a split block
+    // counts on it: all CTAs between a block's first and last contribute), so a count that leaves
+    // fewer items than planned CTAs uses fewer of them.
+    const int G = (int)(I < (int64_t)a.grid_virtual ? (I > 0 ? I : 1) : (int64_t)a.grid_virtual);
     const int64_t i0 = c < G ? I * c / G : 0;
     const int nitems = c < G ? (int)(I * (c + 1) / G - i0) : 0;
     const int cb0 = (int)(i0 / nkb), kb0 = (int)(i0 - (int64_t)cb0 * nkb);
@@ -243,7 +256,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
         const int kq = kb0 + p;
         const int d = kq / nkb;
         const int cb = cb0 + d, kb = kq - d * nkb;
-        if (st < 0 || st >= ns || p < 0 || p >= nitems || cb >= a.ncb) {   // never true for a launch as planned
+        if (st < 0 || st >= ns || p < 0 || p >= nitems || cb >= ncb) {   // never true for a launch as planned
             atomicOr(a.status, ST_BAD_LAUNCH);
             return;
         }
@@ -679,7 +692,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1)
                 if (tidh == 0) {
                     __threadfence();
                     const unsigned done = atomicAdd(a.done_ctr, 1u) + 1u;
-                    if (done == (unsigned)a.ncb) {
+                    if (done == (unsigned)ncb) {
                         atomicExch(a.done_ctr, 0u);           // re-armed for the next launch on this workspace
                         __threadfence_system();               // one fence orders all blocks before all arrivals
                         for (int p = 0; p < a.n_peer; p++)

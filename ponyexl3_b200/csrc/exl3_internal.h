@@ -89,6 +89,7 @@ struct GemvArgs {
     int t_in;                  // input tiles (multiple of 8)
     int t_out_total;           // tile columns of the trellis tensor
     int ncb;                   // logical 128-column blocks to compute
+    const int32_t* ncb_dev;    // optional: the count lives on the device (at most ncb, which the plan is made for)
     int rows;                  // activation rows per block (1..16)
     int x_rows_total;          // rows of the xh matrix (>= xrow + rows of every block)
     int raw_out;               // 1: write fp16(y_inner) without rotation (MoE gate/up)

@@ -14,46 +14,86 @@ struct MoeTableArgs {
     const void* indices;   // (n,) expert of every (token, slot) pair, int32 or int64
     int idx64;
     int n, kk, E, D, H;
+    int e_lo, e_hi;        // experts held here (the stacked tensors hold e_hi - e_lo experts)
     int32_t* blocks_gu;    // (n * 2 * H/128, 4): phys, xrow, sv_off, y_off
     int32_t* row_src_gu;   // (2n,): token of rotated row 2s + p
     int32_t* suh_row_gu;   // (2n,): row of gu_suh (E*2, D) for rotated row 2s + p
     int32_t* blocks_dn;    // (n * D/128, 4)
     int32_t* suh_row_dn;   // (n,): expert of pair s
+    int32_t* counts;       // NULL, or {blocks in use of blocks_gu, of blocks_dn}
 };
 
+constexpr int kMoeOwnedMaxPairs = 2048;
+
+// With an expert range (counts != NULL) only the pairs whose expert is held here get blocks;
+// their blocks are packed to the front of the tables in pair order and the number in use is left
+// on the device for exl3_gemv_blocks_counted.  Rows and outputs keep the numbering of all pairs,
+// so the rows of pairs that are computed elsewhere are simply never touched.
 __global__ void __launch_bounds__(256) moe_decode_tables_kernel(const MoeTableArgs a)
 {
     griddep_launch_dependents();
     griddep_wait();
+    __shared__ short before[kMoeOwnedMaxPairs];   // held pairs in front of pair s
+    __shared__ unsigned char held[kMoeOwnedMaxPairs];
     const int gb = a.H / 128, db = a.D / 128;
     const int n_gu = a.n * 2 * gb, n_dn = a.n * db;
+    const int E_here = a.e_hi - a.e_lo;
     auto expert = [&](int s) -> int {
         const long long e = a.idx64 ? static_cast<const long long*>(a.indices)[s]
                                     : (long long)static_cast<const int*>(a.indices)[s];
         return (int)(e < 0 ? 0 : (e >= a.E ? a.E - 1 : e));       // a bad index must not leave the tensors
     };
+    const bool ranged = a.counts != nullptr;
+    if (ranged) {
+        for (int s = threadIdx.x; s < a.n; s += blockDim.x) {
+            const int e = expert(s);
+            held[s] = e >= a.e_lo && e < a.e_hi;
+        }
+        __syncthreads();
+        for (int s = threadIdx.x; s < a.n; s += blockDim.x) {
+            int q = 0;
+            for (int t = 0; t < s; t++) q += held[t];
+            before[s] = (short)q;
+        }
+        __syncthreads();
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            const int total = before[a.n - 1] + held[a.n - 1];
+            a.counts[0] = total * 2 * gb;
+            a.counts[1] = total * db;
+        }
+    }
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_gu + n_dn; i += gridDim.x * blockDim.x) {
         if (i < n_gu) {
-            const int j = i % gb, sp = i / gb, p = sp & 1, s = sp >> 1, e = expert(s);
-            int4 b;
-            b.x = (p * a.E + e) * gb + j;                   // all gates, then all ups
-            b.y = 2 * s + p;
-            b.z = e * 2 * a.H + p * a.H + 128 * j;
-            b.w = s * 2 * a.H + p * a.H + 128 * j;
-            reinterpret_cast<int4*>(a.blocks_gu)[i] = b;
+            const int j = i % gb, sp = i / gb, p = sp & 1, s = sp >> 1;
+            const int e = expert(s);
+            const bool mine = !ranged || held[s];
+            const int el = mine ? e - a.e_lo : 0;
             if (j == 0) {
                 a.row_src_gu[sp] = s / a.kk;
-                a.suh_row_gu[sp] = 2 * e + p;
+                a.suh_row_gu[sp] = 2 * el + p;
             }
-        } else {
-            const int t = i - n_gu, j = t % db, s = t / db, e = expert(s);
+            if (!mine) continue;
+            const int q = ranged ? before[s] : s;
             int4 b;
-            b.x = e * db + j;
+            b.x = (p * E_here + el) * gb + j;               // all gates, then all ups
+            b.y = 2 * s + p;
+            b.z = el * 2 * a.H + p * a.H + 128 * j;
+            b.w = s * 2 * a.H + p * a.H + 128 * j;
+            reinterpret_cast<int4*>(a.blocks_gu)[(2 * q + p) * gb + j] = b;
+        } else {
+            const int t = i - n_gu, j = t % db, s = t / db;
+            const int e = expert(s);
+            const bool mine = !ranged || held[s];
+            const int el = mine ? e - a.e_lo : 0;
+            if (j == 0) a.suh_row_dn[s] = el;
+            if (!mine) continue;
+            const int q = ranged ? before[s] : s;
+            int4 b;
+            b.x = el * db + j;
             b.y = s;
-            b.z = e * a.D + 128 * j;
+            b.z = el * a.D + 128 * j;
             b.w = s * a.D + 128 * j;
-            reinterpret_cast<int4*>(a.blocks_dn)[t] = b;
-            if (j == 0) a.suh_row_dn[s] = e;
+            reinterpret_cast<int4*>(a.blocks_dn)[q * db + j] = b;
         }
     }
 }
@@ -150,26 +190,50 @@ __global__ void __launch_bounds__(1024) moe_prefill_tables_kernel(const MoePrefi
 
 using namespace exl3;
 
-extern "C" int exl3_moe_decode_tables(const void* indices, int index_bytes, int n_pairs, int top_k,
-                                      int num_experts, int64_t d, int64_t h, int32_t* blocks_gu,
-                                      int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* blocks_dn,
-                                      int32_t* suh_row_dn, unsigned flags, exl3_stream_t stream)
+static int moe_decode_tables_impl(const void* indices, int index_bytes, int n_pairs, int top_k, int num_experts,
+                                  int e_lo, int e_hi, int64_t d, int64_t h, int32_t* blocks_gu,
+                                  int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* blocks_dn,
+                                  int32_t* suh_row_dn, int32_t* counts, unsigned flags, exl3_stream_t stream)
 {
     if (!indices || !blocks_gu || !row_src_gu || !suh_row_gu || !blocks_dn || !suh_row_dn) return EXL3_E_NULL;
     if (index_bytes != 4 && index_bytes != 8) return EXL3_E_DTYPE;
     if (n_pairs < 1 || top_k < 1 || num_experts < 1 || d < 128 || h < 128 || d % 128 || h % 128)
         return EXL3_E_SHAPE;
     if ((int64_t)n_pairs * (2 * h / 128 + d / 128) > (1 << 28)) return EXL3_E_RANGE;
+    if (e_lo < 0 || e_hi <= e_lo || e_hi > num_experts) return EXL3_E_RANGE;
+    if (counts && n_pairs > kMoeOwnedMaxPairs) return EXL3_E_RANGE;
     if (((uintptr_t)blocks_gu | (uintptr_t)blocks_dn) & 15) return EXL3_E_ALIGN;
     MoeTableArgs a;
     a.indices = indices;
     a.idx64 = index_bytes == 8;
     a.n = n_pairs; a.kk = top_k; a.E = num_experts; a.D = (int)d; a.H = (int)h;
+    a.e_lo = e_lo; a.e_hi = e_hi;
     a.blocks_gu = blocks_gu; a.row_src_gu = row_src_gu; a.suh_row_gu = suh_row_gu;
     a.blocks_dn = blocks_dn; a.suh_row_dn = suh_row_dn;
+    a.counts = counts;
     const int total = n_pairs * (int)(2 * h / 128 + d / 128);
     return launch_kernel(moe_decode_tables_kernel, dim3((unsigned)std::min(1024, (total + 255) / 256)), dim3(256), 0,
                          (cudaStream_t)stream, (flags & EXL3_FLAG_PDL) != 0, a);
+}
+
+extern "C" int exl3_moe_decode_tables(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                      int num_experts, int64_t d, int64_t h, int32_t* blocks_gu,
+                                      int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* blocks_dn,
+                                      int32_t* suh_row_dn, unsigned flags, exl3_stream_t stream)
+{
+    return moe_decode_tables_impl(indices, index_bytes, n_pairs, top_k, num_experts, 0, num_experts, d, h,
+                                  blocks_gu, row_src_gu, suh_row_gu, blocks_dn, suh_row_dn, nullptr, flags, stream);
+}
+
+extern "C" int exl3_moe_decode_tables_range(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                            int num_experts, int expert_lo, int expert_hi, int64_t d, int64_t h,
+                                            int32_t* blocks_gu, int32_t* row_src_gu, int32_t* suh_row_gu,
+                                            int32_t* blocks_dn, int32_t* suh_row_dn, int32_t* counts,
+                                            unsigned flags, exl3_stream_t stream)
+{
+    if (!counts) return EXL3_E_NULL;
+    return moe_decode_tables_impl(indices, index_bytes, n_pairs, top_k, num_experts, expert_lo, expert_hi, d, h,
+                                  blocks_gu, row_src_gu, suh_row_gu, blocks_dn, suh_row_dn, counts, flags, stream);
 }
 
 extern "C" int exl3_moe_prefill_tables(const void* indices, int index_bytes, int n_pairs, int top_k,

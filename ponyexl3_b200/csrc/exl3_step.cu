@@ -383,10 +383,11 @@ __global__ void __launch_bounds__(32 * kCombineMaxLanes) attn_combine_kernel(con
 template <int NW> static int launch_attn_partial(const AttnArgs& a, cudaStream_t s, bool pdl)
 {
     const size_t smem = 2 * (size_t)a.nbuf * kAttnTileBytes;
-    static bool set[16] = {};
+    static bool set[kMaxDevices] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 16 && !set[dev]) {
+    if (dev < 0 || dev >= kMaxDevices) return EXL3_E_UNSUPPORTED;
+    if (!set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              4 * kAttnTileBytes);
         if (e != cudaSuccess) return note_cuda(e);
@@ -459,10 +460,12 @@ extern "C" int exl3_swiglu(const uint16_t* gate_up, int64_t gu_row_stride, uint1
 extern "C" size_t exl3_attn_workspace_bytes(int rows, int q_heads, int kv_heads, int64_t total_keys)
 {
     if (rows < 1 || q_heads < 1 || kv_heads < 1 || q_heads % kv_heads || total_keys < 1) return 0;
-    int chunk, nsplit, nbuf;
+    // The number of context chunks depends on the context length through the rounding of the
+    // chunk size, but never exceeds the CTA count the plan aims at: the bound over all contexts,
+    // so that a workspace sized once for the longest context serves every shorter one.
     const int m = q_heads / kv_heads * rows;
-    attn_plan((int)total_keys, kv_heads, m, &chunk, &nsplit, &nbuf);
-    return (size_t)kv_heads * nsplit * m * (128 + 2) * sizeof(float) + 256;
+    const int want = std::max(1, 2 * device_sm_count() / std::max(1, kv_heads));
+    return (size_t)kv_heads * want * m * (128 + 2) * sizeof(float) + 256;
 }
 
 extern "C" int exl3_attn_decode(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache,

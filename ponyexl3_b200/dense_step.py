@@ -5,8 +5,10 @@ the reference hands to mlx_lm (ponyexl3/mlx/model.py:628-634 installs an EXL3Lin
 linear slot; ponyexl3/mlx/exl3_fused.py:92-211 groups q/k/v and gate/up).  Here it exists to
 measure the path in its real setting — 64 layers of q/k/v, o, gate/up, down plus the vocabulary
 head, grouped-query attention over a long KV context between them — with random weights of the
-right shapes.  Every linear runs through the library's GEMV entry points; RMSNorm, RoPE,
-attention and the element-wise glue are PyTorch ops (plumbing around the path, not the path).
+right shapes.  Every linear runs through the library's GEMV entry points; residual + RMSNorm,
+RoPE + cache append, grouped-query attention and the GLU are the library's step kernels
+(exl3_step.cu), so a step is a short train of launches; only the embedding gather and the final
+arg-max are PyTorch ops.
 
 Tensor parallel layout (one process per GPU): every linear is sharded by OUTPUT TILE.
 q/k/v are cut by head, so attention needs no collective; the attention output, the o_proj
@@ -21,7 +23,6 @@ from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
-import torch.nn.functional as F
 
 from .fused import FusedEXL3Group
 from .linear import EXL3Linear
@@ -86,12 +87,10 @@ class SyntheticDenseDecoder:
     over `rows` new positions and returns the arg-max token of every row."""
 
     def __init__(self, cfg: DenseConfig, device: torch.device, seed: int = 5000, group=None,
-                 pdl: bool = True, tensor_parallel: bool = True, native_glue: bool = True,
-                 peer_exchange: bool = True):
+                 pdl: bool = True, tensor_parallel: bool = True, peer_exchange: bool = True):
         self.cfg, self.dev, self.pg = cfg, device, group
-        # native_glue: norm / rotary + cache append / attention / SwiGLU through the library's
-        # step kernels (head_dim 128 only); otherwise the same math as PyTorch ops
-        self.native_glue = native_glue and cfg.head_dim == 128
+        if cfg.head_dim != 128:
+            raise ValueError("the step kernels (rotary, attention) serve head_dim 128 only")
         self.pdl_glue = pdl
         self.world = (dist.get_world_size(group)
                       if (tensor_parallel and dist.is_available() and dist.is_initialized()) else 1)
@@ -101,7 +100,7 @@ class SyntheticDenseDecoder:
         # store their blocks into every rank's row, attention and SwiGLU outputs are copied the same
         # way); otherwise NCCL all-gathers
         self.peer = None
-        if W > 1 and peer_exchange and self.native_glue:
+        if W > 1 and peer_exchange:
             from .parallel import PeerExchange
             self.peer = PeerExchange(cfg.max_rows, max(cfg.intermediate, cfg.q_heads * cfg.head_dim),
                                      group, ring=PeerExchange.ring_for(4 * cfg.layers))
@@ -190,7 +189,6 @@ class SyntheticDenseDecoder:
         ang = pos[:, None] * inv[None, :]
         self.cos = torch.cat([ang.cos(), ang.cos()], dim=-1).to(torch.float16)     # (max_rows, hd)
         self.sin = torch.cat([ang.sin(), ang.sin()], dim=-1).to(torch.float16)
-        self._masks: dict[int, torch.Tensor] = {}
 
     # ---- pieces ------------------------------------------------------------------------------
     @property
@@ -214,39 +212,6 @@ class SyntheticDenseDecoder:
         full = torch.empty((self.world, rows, wmax), dtype=y_local.dtype, device=y_local.device)
         dist.all_gather_into_tensor(full.view(-1), pad.view(-1), group=self.pg)
         return torch.cat([full[r, :, :w] for r, w in enumerate(widths)], dim=1)
-
-    def _rope(self, t: torch.Tensor, rows: int) -> torch.Tensor:
-        """t (rows, heads, hd): rotate-half RoPE at positions context .. context+rows-1."""
-        cos, sin = self.cos[:rows, None, :], self.sin[:rows, None, :]
-        half = t.shape[-1] // 2
-        rot = torch.cat([-t[..., half:], t[..., :half]], dim=-1)
-        return t * cos + rot * sin
-
-    def _mask(self, rows: int) -> torch.Tensor | None:
-        """Row (g, r) of the folded query block sees cache positions <= context + r."""
-        if rows == 1:
-            return None
-        m = self._masks.get(rows)
-        if m is None:
-            c = self.cfg
-            kpos = torch.arange(c.context + rows, device=self.dev)
-            qpos = c.context + torch.arange(rows, device=self.dev)
-            m = (kpos[None, :] <= qpos[:, None]).repeat(c.group, 1)        # (group*rows, L)
-            self._masks[rows] = m
-        return m
-
-    def _attention(self, L: _Layer, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rows: int):
-        """q (rows, hq, hd), k/v (rows, hkv, hd) of the new positions -> (rows, hq*hd)."""
-        c = self.cfg
-        end = c.context + rows
-        L.k_cache[:, c.context:end] = k.transpose(0, 1)
-        L.v_cache[:, c.context:end] = v.transpose(0, 1)
-        # fold the query heads of one KV head into the query length: (1, hkv, group*rows, hd)
-        qf = q.view(rows, self.hkv, c.group, c.head_dim).permute(1, 2, 0, 3).reshape(
-            1, self.hkv, c.group * rows, c.head_dim)
-        out = F.scaled_dot_product_attention(qf, L.k_cache[None, :, :end], L.v_cache[None, :, :end],
-                                             attn_mask=self._mask(rows))
-        return out.view(self.hkv, c.group, rows, c.head_dim).permute(2, 0, 1, 3).reshape(rows, -1)
 
     # ---- the step ----------------------------------------------------------------------------
     def _forward_native(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -296,26 +261,7 @@ class SyntheticDenseDecoder:
     @torch.no_grad()
     def forward_logits(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens (rows,) int64 -> this rank's slice of the logits (rows, local vocab) fp16."""
-        if self.native_glue:
-            return self._forward_native(tokens)
-        c = self.cfg
-        rows = tokens.shape[0]
-        hd = c.head_dim
-        x = self.embed[tokens]                                            # (rows, hidden)
-        for L in self.layers:
-            h = F.rms_norm(x, (c.hidden,), L.norm1, c.rms_eps)
-            q, k, v = L.qkv.forward_all(h)
-            q = self._rope(q.reshape(rows, self.hq, hd), rows)
-            k = self._rope(k.reshape(rows, self.hkv, hd), rows)
-            a = self._attention(L, q, k, v.reshape(rows, self.hkv, hd), rows)
-            a = self._gather(a, [(r * self.hq * hd, (r + 1) * self.hq * hd) for r in range(self.world)])
-            x = x + self._gather(L.o(a), self.hidden_spans)
-            h = F.rms_norm(x, (c.hidden,), L.norm2, c.rms_eps)
-            g, u = L.gate_up.forward_all(h)
-            act = self._gather(F.silu(g) * u, self.inter_spans)
-            x = x + self._gather(L.down(act), self.hidden_spans)
-        h = F.rms_norm(x, (c.hidden,), self.final_norm, c.rms_eps)
-        return self.head(h)
+        return self._forward_native(tokens)
 
     @torch.no_grad()
     def step(self, tokens: torch.Tensor) -> torch.Tensor:

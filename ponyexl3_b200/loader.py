@@ -52,18 +52,24 @@ class EXL3Checkpoint:
         self.storage: dict[str, dict] = {
             key: rec for key, rec in cfg.get("tensor_storage", {}).items()
             if isinstance(rec, dict) and rec.get("quant_format") == "exl3"}
+        # tensor name -> shard.  The index file is taken where it holds good; a tensor it does not
+        # list, or whose shard is missing, is looked for in the shards themselves (top level, then
+        # sub-directories), as the reference does (ponyexl3/ref/loader.py:108-126).
         self._where: dict[str, Path] = {}
         idx_path = self.root / _INDEX
         if idx_path.is_file():
             with open(idx_path) as f:
                 for name, shard in json.load(f).get("weight_map", {}).items():
-                    self._where[name] = self.root / shard
-        else:
-            from safetensors import safe_open
-            for shard in sorted(self.root.glob("*.safetensors")):
-                with safe_open(str(shard), framework="np") as f:
-                    for name in f.keys():
-                        self._where[name] = shard
+                    path = self.root / shard
+                    if path.is_file():
+                        self._where[name] = path
+        from safetensors import safe_open
+        found = sorted(self.root.glob("*.safetensors")) + sorted(
+            p for p in self.root.glob("**/*.safetensors") if p.parent != self.root)
+        for shard in found:
+            with safe_open(str(shard), framework="np") as f:
+                for name in f.keys():
+                    self._where.setdefault(name, shard)
         self._open: dict[Path, object] = {}
 
     # -- tensor access ---------------------------------------------------------------------

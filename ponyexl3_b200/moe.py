@@ -69,10 +69,14 @@ class EXL3SwitchGLU(torch.nn.Module):
         self.pdl = False
 
     # ---- decode: every (token, slot) pair is a one-row problem -------------------------------
-    def _decode(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    def _decode(self, x2d: torch.Tensor, indices: torch.Tensor, expert_range=None) -> torch.Tensor:
         """Three launches: tables, GEMV over (pair, gate|up) blocks, GEMV over (pair, down) blocks
         with the GLU folded into its activation load (the reference's two-launch fused decode,
-        ponyexl3/mlx/exl3_moe.py:345-422).  No host round trip, so the call can be captured."""
+        ponyexl3/mlx/exl3_moe.py:345-422).  No host round trip, so the call can be captured.
+
+        expert_range = (lo, hi, total): this module holds experts lo..hi-1 of `total`, `indices`
+        are global; only the pairs of held experts are computed (their number stays on the device),
+        the rows of all other pairs come back as zeros."""
         from . import _lib
         E, D, H = self.num_experts, self.input_dims, self.hidden_dims
         R, kk = indices.shape
@@ -83,28 +87,52 @@ class EXL3SwitchGLU(torch.nn.Module):
         if idx.dtype not in (torch.int32, torch.int64):
             idx = idx.to(torch.int64)
         idx = idx.contiguous()
-        # one int32 buffer: blocks_gu | blocks_dn | row_src_gu | suh_row_gu | suh_row_dn
+        # one int32 buffer: blocks_gu | blocks_dn | row_src_gu | suh_row_gu | suh_row_dn | counts
         n_gu, n_dn = n * 2 * gb * 4, n * db * 4
-        tab = torch.empty(n_gu + n_dn + 5 * n, dtype=torch.int32, device=dev)
+        tab = torch.empty(n_gu + n_dn + 5 * n + 4, dtype=torch.int32, device=dev)
         blocks_gu, blocks_dn = tab[:n_gu].view(-1, 4), tab[n_gu:n_gu + n_dn].view(-1, 4)
         o = n_gu + n_dn
         row_src, suh_row, sel = tab[o:o + 2 * n], tab[o + 2 * n:o + 4 * n], tab[o + 4 * n:o + 5 * n]
+        counts = tab[o + 5 * n:o + 5 * n + 2]
         flags = _lib.FLAG_PDL if self.pdl else 0
-        _lib.check(_lib.load().exl3_moe_decode_tables(
-            idx.data_ptr(), idx.element_size(), n, kk, E, D, H, blocks_gu.data_ptr(), row_src.data_ptr(),
-            suh_row.data_ptr(), blocks_dn.data_ptr(), sel.data_ptr(), flags,
-            torch.cuda.current_stream(dev).cuda_stream), "exl3_moe_decode_tables")
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        if expert_range is None:
+            _lib.check(_lib.load().exl3_moe_decode_tables(
+                idx.data_ptr(), idx.element_size(), n, kk, E, D, H, blocks_gu.data_ptr(), row_src.data_ptr(),
+                suh_row.data_ptr(), blocks_dn.data_ptr(), sel.data_ptr(), flags, stream), "exl3_moe_decode_tables")
+            cnt_gu = cnt_dn = None
+            new = torch.empty
+        else:
+            lo, hi, total = expert_range
+            if hi - lo != E:
+                raise ValueError("expert_range does not match the experts held here")
+            _lib.check(_lib.load().exl3_moe_decode_tables_range(
+                idx.data_ptr(), idx.element_size(), n, kk, total, lo, hi, D, H, blocks_gu.data_ptr(),
+                row_src.data_ptr(), suh_row.data_ptr(), blocks_dn.data_ptr(), sel.data_ptr(), counts.data_ptr(),
+                flags, stream), "exl3_moe_decode_tables_range")
+            cnt_gu, cnt_dn = counts[0:1], counts[1:2]
+            new = torch.zeros
 
-        ygu = torch.empty((n, 2 * H), dtype=torch.float16, device=dev)
+        ygu = torch.empty((n, 2 * H), dtype=torch.float16, device=dev)   # rows of other ranks' pairs: never read
         ops.gemv_blocks(x2d, xh_rows=2 * n, row_src=row_src, suh=self._gu_suh, suh_row=suh_row,
                         trellis=self._gu_trellis, k=self.k, cb=self.cb, blocks=blocks_gu, rows=1,
-                        svh=self._gu_svh, bias=None, y=ygu, pdl=self.pdl)
+                        svh=self._gu_svh, bias=None, y=ygu, pdl=self.pdl, n_blocks_dev=cnt_gu)
         # the down launch reads [gate | up] as it is and applies the GLU while loading
-        y = torch.empty((n, D), dtype=torch.float16, device=dev)
+        y = new((n, D), dtype=torch.float16, device=dev)
         ops.gemv_blocks(ygu, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=sel,
                         trellis=self._dn_trellis, k=self.k, cb=self.cb, blocks=blocks_dn, rows=1,
-                        svh=self._dn_svh, bias=None, y=y, pdl=self.pdl, glu=self.activation)
+                        svh=self._dn_svh, bias=None, y=y, pdl=self.pdl, glu=self.activation,
+                        n_blocks_dev=cnt_dn)
         return y.view(R, kk, D)
+
+    @torch.no_grad()
+    def decode_range(self, x2d: torch.Tensor, indices: torch.Tensor, expert_range) -> torch.Tensor:
+        """Expert parallelism, few tokens: this module holds experts lo..hi-1 of `total`
+        (expert_range = (lo, hi, total)), `indices` (R, k) are global.  Returns (R, k, D) with the
+        rows of pairs routed elsewhere zero, so the ranks' results add up to the full output."""
+        if indices.shape[0] > DECODE_MAX_TOKENS:
+            raise ValueError("decode_range is for decode-class calls")
+        return self._decode(x2d, indices, expert_range)
 
     # ---- prefill: pairs sorted by expert, tensor-core GEMM over an expert tile table ----------
     @staticmethod

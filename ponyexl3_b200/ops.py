@@ -242,10 +242,12 @@ def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None
                 suh: torch.Tensor | None, suh_row: torch.Tensor | None, trellis: torch.Tensor, k: int,
                 cb: int, blocks: torch.Tensor, rows: int, svh: torch.Tensor | None,
                 bias: torch.Tensor | None, y: torch.Tensor, raw_out: bool = False, pdl: bool = False,
-                fast_accum: bool = False, glu: str | None = None) -> torch.Tensor:
+                fast_accum: bool = False, glu: str | None = None,
+                n_blocks_dev: torch.Tensor | None = None) -> torch.Tensor:
     """Streamed GEMV over a block table (see exl3_gemv_blocks in the header).  `blocks` is an
     int32 CUDA tensor (n_blocks, 4) = phys, xrow, sv_off, y_off; `y` is written in place.
-    glu as in gemv: x2d rows are [gate | up]."""
+    glu as in gemv: x2d rows are [gate | up].  n_blocks_dev: an int32 CUDA scalar with the number of
+    blocks in use (exl3_gemv_blocks_counted); the table's length is then the upper bound."""
     _need_cuda(x2d, "x")
     t_in, t_out_total, _ = trellis.shape
     if x2d.shape[1] != t_in * 16 * (2 if glu is not None else 1):
@@ -258,13 +260,23 @@ def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None
     lib = _lib.load()
     ws = Workspace.get(x2d.device, xh_rows, t_in * 16)
     ptr = lambda t: None if t is None else t.data_ptr()
-    _lib.check(lib.exl3_gemv_blocks(
-        x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),
-        ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), blocks.data_ptr(),
-        blocks.shape[0], rows, ptr(svh), ptr(bias), y.data_ptr(), y.stride(0) if y.ndim == 2 else 0,
-        1 if raw_out else 0, ws.buf.data_ptr(), ws.nbytes,
-        (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0) | _GLU_FLAGS[glu],
-        _stream(x2d.device)), "exl3_gemv_blocks")
+    flags = (_lib.FLAG_PDL if pdl else 0) | (_lib.FLAG_FAST_ACCUM if fast_accum else 0) | _GLU_FLAGS[glu]
+    y_stride = y.stride(0) if y.ndim == 2 else 0
+    if n_blocks_dev is None:
+        _lib.check(lib.exl3_gemv_blocks(
+            x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),
+            ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), blocks.data_ptr(),
+            blocks.shape[0], rows, ptr(svh), ptr(bias), y.data_ptr(), y_stride,
+            1 if raw_out else 0, ws.buf.data_ptr(), ws.nbytes, flags, _stream(x2d.device)), "exl3_gemv_blocks")
+    else:
+        if n_blocks_dev.dtype != torch.int32 or not n_blocks_dev.is_cuda:
+            raise ValueError("n_blocks_dev must be an int32 CUDA tensor")
+        _lib.check(lib.exl3_gemv_blocks_counted(
+            x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),
+            ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), blocks.data_ptr(),
+            blocks.shape[0], n_blocks_dev.data_ptr(), rows, ptr(svh), ptr(bias), y.data_ptr(), y_stride,
+            1 if raw_out else 0, ws.buf.data_ptr(), ws.nbytes, flags, _stream(x2d.device)),
+            "exl3_gemv_blocks_counted")
     return y
 
 

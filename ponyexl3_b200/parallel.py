@@ -127,6 +127,15 @@ class EPSwitchGLU(torch.nn.Module):
         B, S, kk = indices.shape
         D = x.shape[-1]
         flat = indices.reshape(-1)
+        ranged = getattr(self.local, "decode_range", None)
+        if ranged is not None and x.is_cuda and B * S <= 16:
+            # The library picks this rank's pairs on the device (a table of which only the first
+            # entries are in use, their number never seen by the host): nothing here depends on
+            # the routing, so the call — the all-reduce included — can be captured in a CUDA graph.
+            out = ranged(x.reshape(B * S, D), indices.reshape(B * S, kk), (e0, e1, self.num_experts))
+            out = out.reshape(B * S * kk, D)
+            dist.all_reduce(out, group=self.group)
+            return out.reshape(B, S, kk, D)
         mine = (flat >= e0) & (flat < e1)
         out = torch.zeros((B * S * kk, D), dtype=torch.float16, device=x.device)
         sel = torch.nonzero(mine).reshape(-1)                 # pairs this rank computes

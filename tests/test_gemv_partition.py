@@ -72,3 +72,20 @@ def test_partition_rules(ncb, nkb, grid):
     for c in range(grid):
         live = [s[3] for s in segments(c, ncb, nkb, grid) if s[2] < nkb]
         assert len(live) <= 2 and len(set(live)) == len(live)
+
+
+def effective_grid(items: int, planned: int) -> int:
+    """A launch whose block count is read from the device (exl3_gemv_blocks_counted) is planned
+    for the table's length; with fewer items than planned CTAs the kernel uses one CTA per item."""
+    return max(1, min(planned, items))
+
+
+@pytest.mark.parametrize("planned", [1, 7, 296])
+@pytest.mark.parametrize("nkb", [1, 2, 16])
+def test_counted_launch_never_leaves_an_empty_cta_inside_a_split_block(planned, nkb):
+    for ncb in list(range(1, 40)) + [296, 297, 1000]:
+        total = ncb * nkb
+        grid = effective_grid(total, planned)
+        assert grid <= total
+        for c in range(grid):
+            assert total * (c + 1) // grid > total * c // grid

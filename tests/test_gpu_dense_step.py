@@ -74,7 +74,7 @@ def _reference_logits(oracle, dec, tokens, k_caches, v_caches):
 @pytest.mark.parametrize("rows", [1, 4])
 def test_decode_step_matches_cpu_restatement(oracle, rows):
     from ponyexl3_b200.dense_step import DenseConfig, SyntheticDenseDecoder
-    cfg = DenseConfig(layers=2, hidden=256, intermediate=512, q_heads=4, kv_heads=2, head_dim=64,
+    cfg = DenseConfig(layers=2, hidden=512, intermediate=512, q_heads=4, kv_heads=2, head_dim=128,
                       vocab=1024, context=48, max_rows=4, k5_fraction=0.5)
     dev = torch.device("cuda", 0)
     dec = SyntheticDenseDecoder(cfg, dev, seed=11)
@@ -95,7 +95,7 @@ def test_decode_step_matches_cpu_restatement(oracle, rows):
 
 def test_step_is_graph_capturable_and_deterministic():
     from ponyexl3_b200.dense_step import DenseConfig, SyntheticDenseDecoder
-    cfg = DenseConfig(layers=2, hidden=256, intermediate=512, q_heads=4, kv_heads=2, head_dim=64,
+    cfg = DenseConfig(layers=2, hidden=512, intermediate=512, q_heads=4, kv_heads=2, head_dim=128,
                       vocab=1024, context=48, max_rows=4)
     dev = torch.device("cuda", 0)
     dec = SyntheticDenseDecoder(cfg, dev, seed=12)

@@ -194,6 +194,49 @@ def test_config4_4096_tokens_sampled(cuda, oracle):
     assert rel_err(y[toks, slots], want) <= 2e-3
 
 
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("tokens", [1, 5, 16])
+def test_decode_over_an_expert_range_sums_to_the_full_switch(cuda, oracle, world, tokens):
+    """Expert parallelism for few tokens, every rank's share computed one after the other on this
+    GPU: a rank holds a contiguous expert range, the library picks its pairs on the device (the
+    count never reaches the host) and leaves the other pairs' rows zero; the shares add up to the
+    oracle's output, and a captured replay gives the same values."""
+    from ponyexl3_b200 import ops
+    from ponyexl3_b200.parallel import shard_expert_weights, shard_experts
+
+    E, D, H, kk, k = 16, 256, 128, 4, 4
+    w = _experts(E, D, H, k, seed=910 + world)
+    rng = np.random.default_rng(tokens * 10 + world)
+    x = (rng.standard_normal((tokens, D)) * 0.5).astype(np.float16)
+    idx = np.stack([rng.choice(E, size=kk, replace=False) for _ in range(tokens)]).astype(np.int64)
+    xd, idd = torch.from_numpy(x).cuda(), torch.from_numpy(idx).cuda()
+    total = torch.zeros((tokens, kk, D), dtype=torch.float32, device="cuda")
+    nonzero_rows = 0
+    for rank in range(world):
+        e0, e1 = shard_experts(E, world, rank)
+        sw = _switch(shard_expert_weights(w, E, world, rank), k, 0)
+        y = sw.decode_range(xd, idd, (e0, e1, E))
+        held = (idd >= e0) & (idd < e1)
+        assert bool((y[~held] == 0).all())                      # nobody else's rows are touched
+        nonzero_rows += int(held.sum())
+        if rank == 0:                                           # the same call from a CUDA graph
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                sw.decode_range(xd, idd, (e0, e1, E))
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    yg = sw.decode_range(xd, idd, (e0, e1, E))
+                graph.replay()
+                stream.synchronize()
+            assert torch.equal(yg, y)
+        total += y.float()
+    assert nonzero_rows == tokens * kk
+    assert ops.Workspace.get(torch.device("cuda"), 1, 128).status() == 0
+    want = oracle.switch_glu(x, idx, **w, k=k, cb=0)
+    assert rel_err(total.cpu().numpy(), want) <= 2e-3
+
+
 @pytest.mark.parametrize("act", ["silu", "gelu"])
 @pytest.mark.parametrize("rows", [1, 3, 8, 16])
 def test_glu_folded_into_the_down_projection(cuda, oracle, act, rows):

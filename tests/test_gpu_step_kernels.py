@@ -111,12 +111,12 @@ def test_attn_decode_peaked_scores(ops):
 @pytest.mark.parametrize("rows", [1, 4])
 def test_dense_step_native_glue_matches_torch_glue(rows):
     from ponyexl3_b200.dense_step import DenseConfig, SyntheticDenseDecoder
+    from torch_glue_decoder import TorchGlueDecoder
     cfg = DenseConfig(layers=2, hidden=512, intermediate=768, q_heads=4, kv_heads=2, head_dim=128,
                       vocab=1152, context=200, max_rows=4)
     dev = torch.device("cuda", 0)
-    a = SyntheticDenseDecoder(cfg, dev, seed=31, native_glue=True)
-    b = SyntheticDenseDecoder(cfg, dev, seed=31, native_glue=False)
-    assert a.native_glue and not b.native_glue
+    a = SyntheticDenseDecoder(cfg, dev, seed=31)
+    b = TorchGlueDecoder(cfg, dev, seed=31)
     tok = torch.tensor([9, 800, 77, 1000][:rows], device=dev)
     la, lb = a.forward_logits(tok), b.forward_logits(tok)
     assert _rel(la, lb) < 1e-2

@@ -129,3 +129,27 @@ def test_loaded_layer_matches_oracle_forward(tmp_path, oracle):
     y0 = oracle.linear_forward(x, l.trellis, l.k, cb, l.suh, l.svh, l.bias)
     y1 = oracle.linear_forward(x, got.trellis, got.k, cb, got.suh, got.svh, got.bias)
     assert np.array_equal(y0.view(np.uint16), y1.view(np.uint16))
+
+
+def test_partial_index_falls_back_to_scanning_the_shards(tmp_path):
+    """An index that forgets tensors, or names a shard that is gone, must not lose layers: the
+    shards themselves are searched, sub-directories included (ponyexl3/ref/loader.py:108-126)."""
+    import shutil
+
+    save_exl3_layers(tmp_path, LAYERS, shards=3)
+    idx_path = tmp_path / "model.safetensors.index.json"
+    idx = json.loads(idx_path.read_text())
+    victim = LAYERS[0].key
+    # 1. the index forgets every tensor of one layer
+    for name in [n for n in idx["weight_map"] if n.startswith(victim + ".")]:
+        del idx["weight_map"][name]
+    # 2. another layer's shard moves into a sub-directory the index does not know about
+    moved_key = LAYERS[2].key
+    shard = idx["weight_map"][f"{moved_key}.trellis"]
+    idx_path.write_text(json.dumps(idx))
+    (tmp_path / "sub").mkdir()
+    shutil.move(str(tmp_path / shard), str(tmp_path / "sub" / shard))
+    ck = EXL3Checkpoint(tmp_path)
+    assert ck.keys() == sorted(l.key for l in LAYERS)
+    for l in LAYERS:
+        _same(l, ck.layer(l.key))
