@@ -25,6 +25,11 @@ EXL3_API void exl3_tune_gemv(int max_grid, int fuse_x_bytes);
  * multiplies and drains only its first accumulator; 0 = every tile uses both (for comparison). */
 EXL3_API void exl3_tune_gemm(int one_acc_rows);
 
+/* on: 1 = dense prefill GEMMs of 1024 rows and more run on pairs of SMs
+ * (tcgen05.mma.cta_group::2, 512-row output tiles); 0 (default) = the one-CTA kernel for every
+ * shape, which is a little faster on the shapes measured so far. */
+EXL3_API void exl3_tune_gemm_pairs(int on);
+
 #ifdef __cplusplus
 }
 #endif

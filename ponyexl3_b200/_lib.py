@@ -79,6 +79,7 @@ _PROTOTYPES = {
     "exl3_peer_wait": (c_int, [c_void_p, c_uint, c_void_p, c_uint, c_void_p]),
     "exl3_tune_gemv": (None, [c_int, c_int]),
     "exl3_tune_gemm": (None, [c_int]),
+    "exl3_tune_gemm_pairs": (None, [c_int]),
     "exl3_moe_prefill_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
     "exl3_moe_decode_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,

@@ -599,4 +599,9 @@ void exl3_tune_gemm(int one_acc_rows)
     gemm_set_tuning(one_acc_rows);
 }
 
+void exl3_tune_gemm_pairs(int on)
+{
+    gemm_set_pairs(on);
+}
+
 }  // extern "C"

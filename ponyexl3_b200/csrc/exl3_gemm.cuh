@@ -391,15 +391,4 @@ static int launch_gemm_t(GemmArgs a, const __half* xh, const uint32_t* trellis, 
     return check_launch();
 }
 
-template <int K>
-int launch_gemm_k(const GemmArgs& a, int cb, const __half* xh, const uint32_t* trellis, cudaStream_t s)
-{
-    switch (cb) {
-        case CB_3INST: return launch_gemm_t<K, CB_3INST>(a, xh, trellis, s);
-        case CB_MCG: return launch_gemm_t<K, CB_MCG>(a, xh, trellis, s);
-        case CB_MUL1: return launch_gemm_t<K, CB_MUL1>(a, xh, trellis, s);
-        default: return EXL3_E_CODEBOOK;
-    }
-}
-
 }  // namespace exl3

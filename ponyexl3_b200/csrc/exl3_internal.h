@@ -146,7 +146,8 @@ struct GemvPlan {
 };
 GemvPlan gemv_plan(int64_t ncb, int nkb, int rows, bool table, size_t partial_bytes);
 void gemv_set_tuning(int max_grid, int fuse_x_bytes);
-void gemm_set_tuning(int one_acc_rows);                      // benchmark hook, see exl3_b200_tuning.h   // benchmark hook, see exl3_b200_tuning.h
+void gemm_set_tuning(int one_acc_rows);                      // benchmark hook, see exl3_b200_tuning.h
+void gemm_set_pairs(int on);                                 // benchmark hook, see exl3_b200_tuning.h
 
 // ---- prefill GEMM (exl3_gemm.cuh) ---------------------------------------------------------
 struct GemmArgs {

@@ -1,6 +1,7 @@
 // Thin wrappers over the sm_100a tensor-core instructions used by the prefill GEMM:
 // tensor-memory allocation, tcgen05.mma with shared-memory descriptors, commit to an
-// mbarrier, and tensor-memory loads for the epilogue.  cta_group::1 only: one CTA per tile.
+// mbarrier, and tensor-memory loads for the epilogue (cta_group::1; the forms for a pair of
+// CTAs are in exl3_gemm2.cuh).
 #pragma once
 #include <stdint.h>
 

@@ -56,6 +56,29 @@ def test_gemm_all_k_all_codebooks(mod, oracle, k, cb):
     _check(mod, oracle, layer, x)
 
 
+@pytest.mark.parametrize("k,cb,bias", [(4, 0, False), (2, 1, True), (5, 2, False), (8, 0, True), (1, 0, False)])
+@pytest.mark.parametrize("rows,inf,outf", [(1024, 256, 256), (1500, 512, 384), (2049, 128, 640)])
+def test_gemm_on_cta_pairs(mod, oracle, rows, inf, outf, k, cb, bias):
+    """The prefill GEMM on pairs of SMs (tcgen05.mma.cta_group::2, 512-row output tiles, each CTA
+    decoding half of the B tile; selected through the tuning hook): whole and ragged row tiles, a
+    last column tile of 128 columns, several tiles per pair, against the oracle; and the one-CTA
+    kernel gives the same bits."""
+    from ponyexl3_b200 import _lib
+
+    layer = _layer(mod, k, inf, outf, seed=7000 + rows + k, cb=cb, bias=bias)
+    x = np.random.default_rng(rows + k).standard_normal((rows, inf)).astype(np.float16)
+    m = mod.EXL3Linear(layer)
+    xd = torch.from_numpy(x).cuda()
+    y_one = m(xd).clone()
+    _lib.load().exl3_tune_gemm_pairs(1)
+    try:
+        _check(mod, oracle, layer, x)
+        y_pair = m(xd).clone()
+    finally:
+        _lib.load().exl3_tune_gemm_pairs(0)
+    assert torch.equal(y_pair, y_one)
+
+
 @pytest.mark.parametrize("rows", [17, 128, 129, 256, 300, 513])
 def test_gemm_ragged_row_counts(mod, oracle, rows):
     layer = _layer(mod, 4, 512, 256, seed=77)
