@@ -172,6 +172,180 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// ---- the rotation of many rows, on the tensor cores ---------------------------------------------
+// had128(x * suh) for blocks of 16 rows x 128 columns as mma.sync m16n8k16 products with the
+// +-1 Sylvester matrix H[k][n] = (-1)^popcount(k & n): the warp-shuffle butterfly above costs
+// about 130 instructions per row and 128-block and made the prefill GEMM's input rotation
+// instruction-bound at a quarter of the memory bandwidth; here a row and block costs about 40.
+// fp16 inputs times +-1 are exact and the sums are fp32, as in the butterfly; only the order of
+// the fp32 additions differs.
+//
+// A lane loads 16 contiguous bytes (8 columns) of rows g and g + 8 per quarter of the block.
+// The MMA's k index is a free bijection as long as A and B agree: k-step (q, s) takes columns
+// 32 q + 8 t + 4 s + {0, 1} and + {2, 3} of lane t as its k = 2t, 2t+1 and 2t+8, 2t+9.  The
+// matching B fragment is H at those columns against output column n = 8 nt + g: its sign splits
+// into a part that depends on the column's low three bits and g, a part parity(t & nt) that
+// depends on the lane and the low two bits of nt (together sixteen constant registers per lane),
+// and a part parity(q & (nt >> 2)) that is known at compile time and picks one of two
+// accumulators, subtracted at the end: no sign arithmetic is left inside the loop.
+constexpr int kHadTileRow = 272;                 // 256 bytes of a row + 16: the fragment stores hit 32 banks
+constexpr int kHadTileBytes = 16 * kHadTileRow;
+template <typename T> struct Load8;
+template <> struct Load8<__half> {
+    static __device__ __forceinline__ uint4 at(const __half* p) { return *reinterpret_cast<const uint4*>(p); }
+};
+template <> struct Load8<__nv_bfloat16> {
+    static __device__ __forceinline__ uint4 at(const __nv_bfloat16* p)
+    {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            o[i] = h2_as_u32(__floats2half2_rn(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u)));
+        return make_uint4(o[0], o[1], o[2], o[3]);
+    }
+};
+template <> struct Load8<float> {
+    static __device__ __forceinline__ uint4 at(const float* p)
+    {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        return make_uint4(h2_as_u32(__floats2half2_rn(a.x, a.y)), h2_as_u32(__floats2half2_rn(a.z, a.w)),
+                          h2_as_u32(__floats2half2_rn(b.x, b.y)), h2_as_u32(__floats2half2_rn(b.z, b.w)));
+    }
+};
+
+__device__ __forceinline__ uint32_t glu_pair(uint32_t gate, uint32_t up, int glu)
+{
+    const float2 gf = __half22float2(u32_as_h2(gate)), uf = __half22float2(u32_as_h2(up));
+    return h2_as_u32(__floats2half2_rn(glu_value(gf.x, uf.x, glu), glu_value(gf.y, uf.y, glu)));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256, 2)
+    hadamard_mma_kernel(const T* __restrict__ x, int64_t rows, int64_t n, int64_t x_row_stride,
+                        const __half* __restrict__ pre, __half* __restrict__ out,
+                        const int32_t* __restrict__ row_src, const int32_t* __restrict__ pre_row,
+                        const int32_t* __restrict__ rows_dev, int wait_dependency, int glu)
+{
+    griddep_launch_dependents();
+    if (wait_dependency || rows_dev) griddep_wait();
+    if (rows_dev) {           // the number of rows in use was left on the device by an earlier kernel
+        const int64_t r = *rows_dev;
+        rows = r < 0 ? 0 : (r < rows ? r : rows);
+    }
+    __shared__ __align__(16) uint8_t stile[8 * kHadTileBytes];
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    // B fragments, constant per lane: pt[nl][s][j] holds H at columns 4 s + 2 j + {0, 1} of the
+    // lane's 8-column group against output column 8 (4 nh + nl) + g, without the sign of the
+    // quarter (see the loop): the column's low bits meet g, the lane's t meets nl.
+    uint32_t pt[4][2][2];
+#pragma unroll
+    for (int nl = 0; nl < 4; nl++) {
+        const uint32_t flip = (__popc(t & nl) & 1) ? 0x80008000u : 0u;
+#pragma unroll
+        for (int s = 0; s < 2; s++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const uint32_t lo = (__popc((4 * s + 2 * j) & g) & 1) ? 0xBC00u : 0x3C00u;
+                const uint32_t hi = (__popc((4 * s + 2 * j + 1) & g) & 1) ? 0xBC00u : 0x3C00u;
+                pt[nl][s][j] = (lo | (hi << 16)) ^ flip;
+            }
+    }
+    const uint32_t nblk = (uint32_t)(n >> 7);
+    const uint32_t total = (uint32_t)((rows + 15) >> 4) * nblk;
+    const uint32_t warp0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t nwarps = gridDim.x * (blockDim.x >> 5);
+    for (uint32_t blk = warp0; blk < total; blk += nwarps) {
+        const uint32_t rb = blk / nblk, cb = blk - rb * nblk;
+        const int64_t r0 = (int64_t)rb * 16 + g, r1 = r0 + 8;
+        const bool ok0 = r0 < rows, ok1 = r1 < rows;
+        const int64_t col = (int64_t)cb * 128 + 8 * t;
+        uint4 xa[4], xb[4];
+        {
+            const int64_t s0 = ok0 ? (row_src ? row_src[r0] : r0) : 0, s1 = ok1 ? (row_src ? row_src[r1] : r1) : 0;
+            const T* p0 = x + s0 * x_row_stride + col;
+            const T* p1 = x + s1 * x_row_stride + col;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                xa[q] = ok0 ? Load8<T>::at(p0 + 32 * q) : make_uint4(0u, 0u, 0u, 0u);
+                xb[q] = ok1 ? Load8<T>::at(p1 + 32 * q) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (glu) {
+                // the row holds [gate (n) | up (n)]: the input is fp16(act(gate) * up)
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    if (ok0) {
+                        const uint4 u = Load8<T>::at(p0 + n + 32 * q);
+                        xa[q] = make_uint4(glu_pair(xa[q].x, u.x, glu), glu_pair(xa[q].y, u.y, glu),
+                                           glu_pair(xa[q].z, u.z, glu), glu_pair(xa[q].w, u.w, glu));
+                    }
+                    if (ok1) {
+                        const uint4 u = Load8<T>::at(p1 + n + 32 * q);
+                        xb[q] = make_uint4(glu_pair(xb[q].x, u.x, glu), glu_pair(xb[q].y, u.y, glu),
+                                           glu_pair(xb[q].z, u.z, glu), glu_pair(xb[q].w, u.w, glu));
+                    }
+                }
+            }
+        }
+        if (pre) {
+            const __half* q0 = pre + (ok0 && pre_row ? (int64_t)pre_row[r0] * n : 0) + col;
+            const __half* q1 = pre + (ok1 && pre_row ? (int64_t)pre_row[r1] * n : 0) + col;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint4 a = *reinterpret_cast<const uint4*>(q0 + 32 * q);
+                const uint4 b = *reinterpret_cast<const uint4*>(q1 + 32 * q);
+                xa[q].x = h2_as_u32(__hmul2(u32_as_h2(xa[q].x), u32_as_h2(a.x)));
+                xa[q].y = h2_as_u32(__hmul2(u32_as_h2(xa[q].y), u32_as_h2(a.y)));
+                xa[q].z = h2_as_u32(__hmul2(u32_as_h2(xa[q].z), u32_as_h2(a.z)));
+                xa[q].w = h2_as_u32(__hmul2(u32_as_h2(xa[q].w), u32_as_h2(a.w)));
+                xb[q].x = h2_as_u32(__hmul2(u32_as_h2(xb[q].x), u32_as_h2(b.x)));
+                xb[q].y = h2_as_u32(__hmul2(u32_as_h2(xb[q].y), u32_as_h2(b.y)));
+                xb[q].z = h2_as_u32(__hmul2(u32_as_h2(xb[q].z), u32_as_h2(b.z)));
+                xb[q].w = h2_as_u32(__hmul2(u32_as_h2(xb[q].w), u32_as_h2(b.w)));
+            }
+        }
+        // The accumulator fragments (4 bytes per lane, row and 8-column group) go through a padded
+        // tile in shared memory so that every lane stores 16 contiguous bytes: 8 instead of 32
+        // stores, and whole 32-byte sectors.
+        uint8_t* tile = stile + (threadIdx.x >> 5) * kHadTileBytes;
+#pragma unroll
+        for (int nh = 0; nh < 4; nh++)
+#pragma unroll
+            for (int nl = 0; nl < 4; nl++) {
+                // output columns 8 nt + g, nt = 4 nh + nl: quarter q enters with the sign
+                // parity(q & nh), known at compile time, so it picks one of two accumulators
+                float cp[4] = {0.f, 0.f, 0.f, 0.f}, cm[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const uint32_t a0[4] = {xa[q].x, xb[q].x, xa[q].y, xb[q].y};
+                    const uint32_t a1[4] = {xa[q].z, xb[q].z, xa[q].w, xb[q].w};
+                    if (((q & nh) == 1) || ((q & nh) == 2)) {       // odd number of common bits
+                        mma_16816(cm, a0, pt[nl][0][0], pt[nl][0][1]);
+                        mma_16816(cm, a1, pt[nl][1][0], pt[nl][1][1]);
+                    } else {
+                        mma_16816(cp, a0, pt[nl][0][0], pt[nl][0][1]);
+                        mma_16816(cp, a1, pt[nl][1][0], pt[nl][1][1]);
+                    }
+                }
+                const int nt = 4 * nh + nl;
+                *reinterpret_cast<__half2*>(tile + g * kHadTileRow + 16 * nt + 4 * t) =
+                    __floats2half2_rn((cp[0] - cm[0]) * EXL3_HAD_SCALE, (cp[1] - cm[1]) * EXL3_HAD_SCALE);
+                *reinterpret_cast<__half2*>(tile + (g + 8) * kHadTileRow + 16 * nt + 4 * t) =
+                    __floats2half2_rn((cp[2] - cm[2]) * EXL3_HAD_SCALE, (cp[3] - cm[3]) * EXL3_HAD_SCALE);
+            }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; i++) {          // 16 rows x 16 chunks of 16 bytes, two rows per turn
+            const int rr = 2 * i + (lane >> 4), ch = lane & 15;
+            const int64_t r = (int64_t)rb * 16 + rr;
+            const uint4 v = *reinterpret_cast<const uint4*>(tile + rr * kHadTileRow + 16 * ch);
+            if (r < rows) *reinterpret_cast<uint4*>(out + r * n + (int64_t)cb * 128 + 8 * ch) = v;
+        }
+        __syncwarp();
+    }
+}
+
 // ---- launchers ------------------------------------------------------------------------------
 
 static int grid_for(int64_t warps_needed, int warps_per_block)
@@ -248,10 +422,17 @@ int launch_table(int cb, __half* table, cudaStream_t s)
 int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
                     const __half* pre, const __half* post, __half* out, const int32_t* row_src,
                     const int32_t* pre_row, const int32_t* post_row, bool pdl, int out_mode,
-                    cudaStream_t s, int glu)
+                    cudaStream_t s, int glu, const int32_t* rows_dev)
 {
     if (rows * (n >> 7) >= ((int64_t)1 << 31)) return EXL3_E_RANGE;   // the kernel counts blocks in 32 bits
-    const int g = grid_for(rows * (n >> 7), 8);
+    // Many rows into a plain fp16 matrix (the prefill GEMM's operand): 16-row blocks on the tensor cores.
+    // (a GLU over bf16 / fp32 rows stays on the butterfly kernel, which applies it before the fp16 rounding)
+    const bool mma = out_mode == HAD_OUT_F16 && !post && !post_row && rows >= kHadamardMmaMinRows &&
+                     (!glu || x_dtype == EXL3_DT_F16) &&
+                     x_row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                     (!pre || (reinterpret_cast<uintptr_t>(pre) & 15) == 0) && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    if (rows_dev && !mma) return EXL3_E_UNSUPPORTED;
+    const int g = mma ? grid_for(((rows + 15) >> 4) * (n >> 7), 8) : grid_for(rows * (n >> 7), 8);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(g);
     cfg.blockDim = dim3(256);
@@ -264,6 +445,24 @@ int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t
     cfg.numAttrs = pdl ? 1 : 0;
     const int wait = pdl ? 1 : 0;
     cudaError_t e;
+    if (mma) {
+        switch (x_dtype) {
+            case EXL3_DT_F16:
+                e = cudaLaunchKernelEx(&cfg, hadamard_mma_kernel<__half>, (const __half*)x, rows, n, x_row_stride, pre,
+                                       out, row_src, pre_row, rows_dev, wait, glu);
+                break;
+            case EXL3_DT_BF16:
+                e = cudaLaunchKernelEx(&cfg, hadamard_mma_kernel<__nv_bfloat16>, (const __nv_bfloat16*)x, rows, n,
+                                       x_row_stride, pre, out, row_src, pre_row, rows_dev, wait, glu);
+                break;
+            case EXL3_DT_F32:
+                e = cudaLaunchKernelEx(&cfg, hadamard_mma_kernel<float>, (const float*)x, rows, n, x_row_stride, pre,
+                                       out, row_src, pre_row, rows_dev, wait, glu);
+                break;
+            default: return EXL3_E_DTYPE;
+        }
+        return note_cuda(e);
+    }
     switch (x_dtype) {
         case EXL3_DT_F16:
             e = cudaLaunchKernelEx(&cfg, hadamard_kernel<__half>, (const __half*)x, rows, n,

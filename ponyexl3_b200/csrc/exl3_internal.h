@@ -62,10 +62,11 @@ int launch_table(int cb, __half* table, cudaStream_t s);
 // Output forms of the rotation kernel: plain fp16, or one 32-bit word per element holding
 // (x, 0) / (x, x) for the GEMV's two-slot activation fragments.
 enum : int { HAD_OUT_F16 = 0, HAD_OUT_PAIR_X0 = 1, HAD_OUT_PAIR_XX = 2 };
+constexpr int kHadamardMmaMinRows = 64;   // from here on the rotation runs on the tensor cores (16-row blocks)
 int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t x_row_stride,
                     const __half* pre, const __half* post, __half* out, const int32_t* row_src,
                     const int32_t* pre_row, const int32_t* post_row, bool pdl, int out_mode,
-                    cudaStream_t s, int glu = 0);   // glu: x rows are [gate (n) | up (n)], see glu_value
+                    cudaStream_t s, int glu = 0, const int32_t* rows_dev = nullptr);   // glu: x rows are [gate (n) | up (n)], see glu_value
 
 // One logical 128-column output block of a streamed GEMV: where its weights, activations,
 // output scales and results live.  NULL descriptor table = the identity mapping of a plain

@@ -103,6 +103,24 @@ def test_hadamard_matches_oracle(ops, oracle, golden, dtype):
         assert d.max() <= 1
 
 
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16", "float32"])
+@pytest.mark.parametrize("rows,n", [(64, 128), (200, 384), (1031, 256)])
+def test_hadamard_of_many_rows_on_the_tensor_cores(ops, oracle, dtype, rows, n):
+    """From 64 rows on the rotation runs as 16-row blocks of mma products with the +-1 matrix
+    (whole and ragged row blocks, with and without the input scale); same values as the oracle
+    up to the float32 summation order: at most one fp16 ulp apart, and rarely."""
+    rng = np.random.default_rng(rows + n)
+    x = rng.standard_normal((rows, n)).astype(np.float32)
+    pre = np.where(rng.random(n) > 0.5, -1.0, 1.0).astype(np.float16)
+    xt = torch.from_numpy(x).cuda().to(getattr(torch, dtype))
+    xin = xt.to(torch.float16).cpu().numpy()
+    for kw_np, kw_t in (({}, {}), (dict(pre_scale=pre), dict(pre_scale=torch.from_numpy(pre).cuda()))):
+        want = oracle.had_r_128(xin.astype(np.float32), **kw_np).astype(np.float16)
+        got = ops.had_r_128(xt, **kw_t).cpu().numpy()
+        d = np.abs(got.view(np.int16).astype(np.int32) - want.view(np.int16).astype(np.int32))
+        assert d.max() <= 1 and (d > 0).mean() < 0.01
+
+
 def test_hadamard_strided_rows_and_errors(ops, oracle):
     rng = np.random.default_rng(2)
     big = torch.from_numpy(rng.standard_normal((5, 512)).astype(np.float16)).cuda()
