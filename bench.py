@@ -844,8 +844,7 @@ def run_moe(args):
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     from ponyexl3_b200 import ops
     from ponyexl3_b200.moe import EXL3SwitchGLU, route_topk
-    from ponyexl3_b200.parallel import (EPSwitchGLU, dispatch_rows_to_experts, return_rows_to_tokens,
-                                        shard_expert_weights)
+    from ponyexl3_b200.parallel import EPSwitchGLU, shard_expert_weights
 
     E, D, H, kk, k, T = 256, 2048, 512, 8, 4, args.tokens
     g = torch.Generator(device=dev)
@@ -869,17 +868,15 @@ def run_moe(args):
             step = lambda: ep(x.view(1, T, D), inds.view(1, T, kk))
             mode = f"ep{world}: tokens replicated, pairs picked on the device, all-reduce of partial outputs, one CUDA graph"
         else:
+            if T % world:
+                raise SystemExit("--tokens must be a multiple of the number of GPUs")
             t0, t1 = T * rank // world, T * (rank + 1) // world
             xl, il = x[t0:t1].contiguous(), inds[t0:t1].contiguous()
-
-            def step():
-                rows, e_local, book = dispatch_rows_to_experts(xl, il, E)
-                if rows.shape[0]:
-                    yr = local_sw(rows.reshape(1, -1, D), e_local.reshape(1, -1, 1)).reshape(-1, D)
-                else:
-                    yr = torch.empty((0, D), dtype=torch.float16, device=dev)
-                return return_rows_to_tokens(yr, book)
-            mode = f"ep{world}: tokens partitioned, two all-to-alls"
+            ep = EPSwitchGLU(local_sw, E)
+            step = lambda: ep.forward_partitioned(xl, il)
+            mode = (f"ep{world}: tokens partitioned; all-gather of tokens and routing, every rank computes the pairs of "
+                    "its experts (picked on the device) and stores the outputs into the owners' memory over NVLink; "
+                    "two CUDA graphs replayed in turn")
 
     def barrier():
         if dist is not None:
@@ -887,19 +884,27 @@ def run_moe(args):
         torch.cuda.synchronize()
 
     stream = torch.cuda.Stream(device=dev)
-    graph = None
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
-        # No host round trip anywhere on one GPU, nor for few tokens under expert parallelism (each
-        # rank's pairs are picked on the device): the call is captured, the all-reduce included.
-        # Many tokens under expert parallelism exchange rows with host-visible split sizes: eager.
-        if (world == 1 or T <= 16) and not args.no_graph:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step()
-        run = graph.replay if graph is not None else step
+        # No host round trip anywhere: the call is captured, the collectives included.  Expert
+        # parallelism over many tokens rotates its exchange buffers per call, so two graphs (two
+        # consecutive calls) are captured and replayed in turn.
+        graphs = []
+        if not args.no_graph:
+            for _ in range(2 if (world > 1 and T > 16) else 1):
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=stream):
+                    step()
+                graphs.append(gr)
+        turn = [0]
+
+        def run():
+            if not graphs:
+                return step()
+            graphs[turn[0] % len(graphs)].replay()
+            turn[0] += 1
         for _ in range(3):
             run()
         barrier()
@@ -978,7 +983,7 @@ def run_moe(args):
             "config": {"workload": f"configs[3]: SwitchGLU, {E} experts, top-{kk}, hidden {D}, intermediate {H}, "
                                    f"K={k}, {T} tokens", "tokens": T, "experts_touched": touched,
                        "packed_bytes_touched": packed, "flops": flops, "parallelism": mode,
-                       "launch": "cuda_graph" if graph is not None else "eager"},
+                       "launch": "cuda_graph" if graphs else "eager"},
             "roofline": ({"bound": "hbm", "achieved": packed / (ms * 1e-3) / 1e9 / world, "peak": hbm_peak,
                           "unit": "GB/s", "frac": packed / (ms * 1e-3) / 1e9 / world / hbm_peak, "traffic": None,
                           "peak_kind": f"of {kind}"} if few else

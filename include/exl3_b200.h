@@ -62,7 +62,7 @@ extern "C" {
                                    instead of rounding their sum to fp16 first.  Saves one
                                    instruction per weight; outputs move by < 2e-4 relative */
 
-#define EXL3_FLAG_GLU_SILU 4u   /* exl3_gemv, exl3_gemv_blocks, exl3_gemv_noalloc: every x row holds */
+#define EXL3_FLAG_GLU_SILU 4u   /* exl3_gemv, exl3_gemv_blocks, exl3_gemv_noalloc, exl3_gemm_tiles: every x row holds */
 #define EXL3_FLAG_GLU_GELU 8u   /* [gate (in) | up (in)] (x_row_stride >= 2*in) and the layer's input is
                                    fp16(silu(gate) * up) / fp16(gelu_tanh(gate) * up), computed while x
                                    is read: the down projection of a gated MLP or of a SwitchGLU takes
@@ -195,6 +195,23 @@ EXL3_API int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, i
                     const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
                     int64_t y_row_stride, const int32_t* y_row_map, void* workspace, size_t workspace_bytes,
                     unsigned flags, exl3_stream_t stream);
+
+/* exl3_gemm_tiles for expert parallelism.  xh_rows_dev (may be NULL): device int32 with the
+ * number of rotated rows in use, at most xh_rows (only those are rotated; the tile table refers
+ * to no others).  n_peers > 0: the output rows are spread over n_peers GPUs — y_row_map is
+ * required and gives a GLOBAL row, row r lives in row r % rows_per_peer of the buffer
+ * y_peers[r / rows_per_peer] (host array of device addresses, peer-mapped, y_row_stride apart);
+ * the epilogue stores straight into the owner's memory, and when the whole grid has stored its
+ * tiles every GPU's arrival counter (counter_peers, as in exl3_gemv_peers) gets one arrival, so
+ * a GPU's rows are complete after n_peers arrivals (exl3_peer_wait).  y is ignored then.
+ * EXL3_FLAG_GLU_* as in exl3_gemv: x rows are [gate | up]. */
+EXL3_API int exl3_gemm_tiles_peers(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                          const int32_t* xh_rows_dev, const int32_t* row_src, const uint16_t* suh,
+                          const int32_t* suh_row, const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k,
+                          int cb, const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
+                          int64_t y_row_stride, const int32_t* y_row_map, const uint64_t* y_peers,
+                          const uint64_t* counter_peers, int n_peers, int64_t rows_per_peer, void* workspace,
+                          size_t workspace_bytes, unsigned flags, exl3_stream_t stream);
 
 /* exl3_gemv without a caller-supplied workspace, for callers that cannot allocate device
  * memory: operator slots of a serving framework or thin language bindings that are handed
@@ -342,7 +359,10 @@ EXL3_API int exl3_moe_decode_tables_range(const void* indices, int index_bytes, 
  * two experts, and expanded into the tile tables exl3_gemm_tiles takes — the reference builds the
  * same expert block table on the host, ponyexl3/mlx/exl3_moe.py:79-99,685-768.
  *   order (n_pairs): sorted position -> pair (the y_row_map of the down launch);
- *   row_src_gu, suh_row_gu (2*n_pairs): rotated rows [0,n) carry the gate signs, [n,2n) the up signs;
+ *   row_src_gu, suh_row_gu (2*n_pairs): the rotated rows of the gate/up launch; an expert with
+ *     sorted positions [seg, seg + cnt) has its gate rows at [2 seg, 2 seg + cnt) and its up rows
+ *     at [2 seg + cnt, 2 seg + 2 cnt), and both kinds of tiles store to the [gate | up] row of
+ *     the sorted position;
  *   suh_row_dn (n_pairs); tiles_gu (2 * slots * ceil(h/256), 8): gate tiles then up tiles;
  *   tiles_dn (slots * ceil(d/256), 8); slots = n_pairs / 256 + num_experts (unused ones are empty).
  * n_pairs <= 2^20, num_experts <= 1024. */
@@ -351,6 +371,17 @@ EXL3_API int exl3_moe_prefill_tables(const void* indices, int index_bytes, int n
                                      int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* suh_row_dn,
                                      int32_t* tiles_gu, int32_t* tiles_dn, unsigned flags,
                                      exl3_stream_t stream);
+
+/* Expert parallelism, many tokens (every GPU sees all tokens' routing, the stacked tensors hold
+ * experts expert_lo .. expert_hi-1 of num_experts): only the pairs routed to a held expert are
+ * sorted and tiled; counts (device int32[2]) receives the rotated gate/up rows in use (2 x held
+ * pairs) and the sorted positions in use, for exl3_gemm_tiles_peers.  slots = n_pairs / 256 +
+ * (expert_hi - expert_lo). */
+EXL3_API int exl3_moe_prefill_tables_range(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                           int num_experts, int expert_lo, int expert_hi, int64_t d, int64_t h,
+                                           int32_t* order, int32_t* row_src_gu, int32_t* suh_row_gu,
+                                           int32_t* suh_row_dn, int32_t* tiles_gu, int32_t* tiles_dn,
+                                           int32_t* counts, unsigned flags, exl3_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -56,6 +56,10 @@ _PROTOTYPES = {
     "exl3_gemm_tiles": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64,
                                 c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_size_t, c_uint, c_void_p]),
+    "exl3_gemm_tiles_peers": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
+                                      c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p,
+                                      c_size_t, c_uint, c_void_p]),
     "exl3_gemv_noalloc": (c_int, [c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_int64, c_int,
                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_uint,
                                   c_void_p]),
@@ -84,6 +88,9 @@ _PROTOTYPES = {
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
     "exl3_moe_decode_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_uint, c_void_p]),
+    "exl3_moe_prefill_tables_range": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_uint, c_void_p]),
     "exl3_moe_decode_tables_range": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_uint, c_void_p]),

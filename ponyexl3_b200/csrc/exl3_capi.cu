@@ -528,14 +528,21 @@ int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_stride, co
     return launch_gemm(a, k, cb, xh, reinterpret_cast<const uint32_t*>(trellis), s);
 }
 
-int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
-                    const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
-                    const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
-                    const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
-                    int64_t y_row_stride, const int32_t* y_row_map, void* workspace, size_t workspace_bytes,
-                    unsigned flags, exl3_stream_t stream)
+struct TilePeers {
+    const int32_t* xh_rows_dev = nullptr;   // rotated rows in use, on the device (NULL: all xh_rows)
+    int n = 0;                              // GPUs the output rows are spread over (0: plain local y)
+    int64_t rows_per_peer = 0;
+    const uint64_t* y = nullptr;            // host arrays of device pointers
+    const uint64_t* ctr = nullptr;
+};
+
+static int gemm_tiles_impl(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                           const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                           const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                           const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
+                           int64_t y_row_stride, const int32_t* y_row_map, void* workspace, size_t workspace_bytes,
+                           unsigned flags, exl3_stream_t stream, const TilePeers& peers)
 {
-    (void)flags;
     if (!x || !trellis || !y || !tiles) return EXL3_E_NULL;
     if (k < 1 || k > 8) return EXL3_E_K;
     if (cb < 0 || cb > 2) return EXL3_E_CODEBOOK;
@@ -544,7 +551,8 @@ int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh
     if (xh_rows < 1 || xh_rows > (1 << 30)) return EXL3_E_ROWS;
     if (n_tiles < 0 || n_tiles > (1 << 24)) return EXL3_E_SHAPE;
     const int64_t in = 16 * t_in;
-    if (x_row_stride < in) return EXL3_E_SHAPE;
+    const int glu = glu_mode(flags);
+    if (x_row_stride < (glu ? 2 * in : in)) return EXL3_E_SHAPE;
     int rc = check_dtype_align(x, x_dtype, x_row_stride);
     if (rc) return rc;
     if (!aligned(trellis, 16) || !aligned(y, 16) || y_row_stride % 8 || !aligned(tiles, 16))
@@ -553,13 +561,16 @@ int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh
     if (!workspace) return EXL3_E_WORKSPACE;
     if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
     if (workspace_bytes < exl3_gemm_workspace_bytes(xh_rows, in)) return EXL3_E_WORKSPACE;
+    if (peers.n < 0 || peers.n > kMaxPeers) return EXL3_E_RANGE;
+    if (peers.n > 0 && (!peers.y || !peers.ctr || peers.rows_per_peer < 1 || peers.rows_per_peer > (1 << 30) || !y_row_map))
+        return EXL3_E_NULL;
     if (n_tiles == 0) return EXL3_OK;
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     __half* xh = reinterpret_cast<__half*>(ws + kWsScratch);
     cudaStream_t s = (cudaStream_t)stream;
     rc = launch_hadamard(x, x_dtype, xh_rows, in, x_row_stride, reinterpret_cast<const __half*>(suh),
-                         nullptr, xh, row_src, suh_row, nullptr, false, HAD_OUT_F16, s);
+                         nullptr, xh, row_src, suh_row, nullptr, false, HAD_OUT_F16, s, glu, peers.xh_rows_dev);
     if (rc) return rc;
     GemmArgs a = {};
     a.svh = reinterpret_cast<const __half*>(svh);
@@ -574,7 +585,48 @@ int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh
     a.m = (int)xh_rows;
     a.t_in = (int)t_in;
     a.t_out = (int)t_out_total;
+    a.n_peer = peers.n;
+    a.rows_per_peer = (int)peers.rows_per_peer;
+    a.done_ctr = reinterpret_cast<unsigned*>(ws + kWsDoneCtr);
+    for (int p = 0; p < peers.n; p++) {
+        if (!peers.y[p] || !peers.ctr[p]) return EXL3_E_NULL;
+        if (peers.y[p] % 16 || peers.ctr[p] % 4) return EXL3_E_ALIGN;
+        a.y_peer[p] = reinterpret_cast<__half*>(peers.y[p]);
+        a.ctr_peer[p] = reinterpret_cast<unsigned*>(peers.ctr[p]);
+    }
     return launch_gemm(a, k, cb, xh, reinterpret_cast<const uint32_t*>(trellis), s);
+}
+
+int exl3_gemm_tiles(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                    const int32_t* row_src, const uint16_t* suh, const int32_t* suh_row,
+                    const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k, int cb,
+                    const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
+                    int64_t y_row_stride, const int32_t* y_row_map, void* workspace, size_t workspace_bytes,
+                    unsigned flags, exl3_stream_t stream)
+{
+    return gemm_tiles_impl(x, x_dtype, x_row_stride, xh_rows, row_src, suh, suh_row, trellis, t_in, t_out_total, k,
+                           cb, tiles, n_tiles, svh, y, y_row_stride, y_row_map, workspace, workspace_bytes, flags,
+                           stream, TilePeers{});
+}
+
+int exl3_gemm_tiles_peers(const void* x, int x_dtype, int64_t x_row_stride, int64_t xh_rows,
+                          const int32_t* xh_rows_dev, const int32_t* row_src, const uint16_t* suh,
+                          const int32_t* suh_row, const uint16_t* trellis, int64_t t_in, int64_t t_out_total, int k,
+                          int cb, const int32_t* tiles, int64_t n_tiles, const uint16_t* svh, uint16_t* y,
+                          int64_t y_row_stride, const int32_t* y_row_map, const uint64_t* y_peers,
+                          const uint64_t* counter_peers, int n_peers, int64_t rows_per_peer, void* workspace,
+                          size_t workspace_bytes, unsigned flags, exl3_stream_t stream)
+{
+    TilePeers p;
+    p.xh_rows_dev = xh_rows_dev;
+    p.n = n_peers;
+    p.rows_per_peer = rows_per_peer;
+    p.y = y_peers;
+    p.ctr = counter_peers;
+    if (n_peers > 0 && !y) y = reinterpret_cast<uint16_t*>(y_peers ? y_peers[0] : 0);
+    return gemm_tiles_impl(x, x_dtype, x_row_stride, xh_rows, row_src, suh, suh_row, trellis, t_in, t_out_total, k,
+                           cb, tiles, n_tiles, svh, y, y_row_stride, y_row_map, workspace, workspace_bytes, flags,
+                           stream, p);
 }
 
 #ifdef EXL3_PROFILE

@@ -301,7 +301,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     had128_regs(v);
                     if (row < ti.m_end) {
                         const int orow = a.y_row_map ? a.y_row_map[row + ti.y_row_delta] : row + ti.y_row_delta;
-                        __half* yp = a.y + (int64_t)orow * a.y_row_stride + col0;
+                        __half* yp;
+                        if (a.n_peer > 0) {      // the row belongs to the GPU that holds its token
+                            const int pr = orow / a.rows_per_peer;
+                            yp = a.y_peer[pr] + (int64_t)(orow - pr * a.rows_per_peer) * a.y_row_stride + col0;
+                        } else {
+                            yp = a.y + (int64_t)orow * a.y_row_stride + col0;
+                        }
 #pragma unroll
                         for (int c = 0; c < 16; c++) {
                             float o[8];
@@ -345,6 +351,20 @@ done:
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
+    }
+    if (a.n_peer > 0 && tid == 0) {
+        // Rows were stored into other GPUs' memory: every CTA is counted on a local counter (the
+        // barrier above orders the CTA's stores before this thread's fence), and the CTA that
+        // completes the count announces this GPU's rows to every peer — one system-scope fence
+        // and one arrival per peer for the whole grid.
+        __threadfence();
+        const unsigned done = atomicAdd(a.done_ctr, 1u) + 1u;
+        if (done == gridDim.x) {
+            atomicExch(a.done_ctr, 0u);           // re-armed for the next launch on this workspace
+            __threadfence_system();
+            for (int p = 0; p < a.n_peer; p++)
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(a.ctr_peer[p]) : "memory");
+        }
     }
 }
 

@@ -167,6 +167,14 @@ struct GemmArgs {
     int stages;
     int one_acc_rows;         // tiles with at most this many rows use only the first accumulator
     uint32_t cb_xor;
+    // grouped launches whose output rows live on several GPUs (expert parallelism): output row r
+    // (after y_row_map) is row r % rows_per_peer of y_peer[r / rows_per_peer]; when the whole grid
+    // is done, every peer's counter gets one arrival
+    int n_peer;
+    int rows_per_peer;
+    __half* y_peer[kMaxPeers];
+    unsigned* ctr_peer[kMaxPeers];
+    unsigned* done_ctr;       // local: CTAs that have stored all their tiles
 };
 
 int launch_gemm(const GemmArgs& a, int k, int cb, const __half* xh, const uint32_t* trellis,

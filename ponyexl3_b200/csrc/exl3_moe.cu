@@ -104,18 +104,26 @@ struct MoePrefillArgs {
     const void* indices;
     int idx64;
     int n, kk, E, D, H, slots;
+    int e_lo, e_hi;        // experts held here; pairs of other experts get no rows
     int32_t* order;        // (n,): sorted position -> pair
     int32_t* row_src_gu;   // (2n,)
     int32_t* suh_row_gu;   // (2n,)
     int32_t* suh_row_dn;   // (n,)
     int32_t* tiles_gu;     // (2 * slots * ceil(H/256), 8)
     int32_t* tiles_dn;     // (slots * ceil(D/256), 8)
+    int32_t* counts;       // NULL, or {rotated gate/up rows in use, sorted positions in use}
 };
 
 constexpr int kMoeMaxExperts = 1024;
 
 // One CTA: shared-memory histogram, scan, scatter.  32 K pairs take a few microseconds; the
 // tables are tiny next to the GEMMs they drive.
+//
+// Row layout.  The held pairs are sorted by expert; expert e owns sorted positions
+// [seg, seg + cnt).  The rotated rows of the gate/up launch keep an expert's rows together —
+// gate rows [2 seg, 2 seg + cnt), then up rows [2 seg + cnt, 2 seg + 2 cnt) — so the rows in use
+// are the first 2 x (held pairs) and a launch that reads their number from the device skips the
+// rest.  Gate and up tiles store to the [gate | up] row of the sorted position.
 __global__ void __launch_bounds__(1024) moe_prefill_tables_kernel(const MoePrefillArgs a)
 {
     griddep_launch_dependents();
@@ -123,35 +131,47 @@ __global__ void __launch_bounds__(1024) moe_prefill_tables_kernel(const MoePrefi
     __shared__ int count[kMoeMaxExperts], seg[kMoeMaxExperts], blk0[kMoeMaxExperts], cursor[kMoeMaxExperts];
     __shared__ int total_blocks;
     const int tid = threadIdx.x;
-    auto expert = [&](int s) -> int {
+    const int E_here = a.e_hi - a.e_lo;
+    auto expert = [&](int s) -> int {       // local index of the pair's expert, -1: not held here
         const long long e = a.idx64 ? static_cast<const long long*>(a.indices)[s]
                                     : (long long)static_cast<const int*>(a.indices)[s];
-        return (int)(e < 0 ? 0 : (e >= a.E ? a.E - 1 : e));
+        const int ec = (int)(e < 0 ? 0 : (e >= a.E ? a.E - 1 : e));      // a bad index must not leave the tensors
+        return ec >= a.e_lo && ec < a.e_hi ? ec - a.e_lo : -1;
     };
-    for (int e = tid; e < a.E; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
+    for (int e = tid; e < E_here; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
     __syncthreads();
-    for (int s = tid; s < a.n; s += blockDim.x) atomicAdd(&count[expert(s)], 1);
+    for (int s = tid; s < a.n; s += blockDim.x) {
+        const int e = expert(s);
+        if (e >= 0) atomicAdd(&count[e], 1);
+    }
     __syncthreads();
     if (tid == 0) {                       // E <= 1024: a serial scan is a microsecond
         int rows = 0, blocks = 0;
-        for (int e = 0; e < a.E; e++) {
+        for (int e = 0; e < E_here; e++) {
             seg[e] = rows;
             blk0[e] = blocks;
             rows += count[e];
             blocks += (count[e] + 255) >> 8;
         }
         total_blocks = blocks;
+        if (a.counts) {
+            a.counts[0] = 2 * rows;
+            a.counts[1] = rows;
+        }
     }
     __syncthreads();
     for (int s = tid; s < a.n; s += blockDim.x) {
         const int e = expert(s);
-        const int pos = seg[e] + atomicAdd(&cursor[e], 1);
+        if (e < 0) continue;
+        const int i = atomicAdd(&cursor[e], 1);
+        const int pos = seg[e] + i;
         a.order[pos] = s;
         const int tok = s / a.kk;
-        a.row_src_gu[pos] = tok;
-        a.row_src_gu[a.n + pos] = tok;
-        a.suh_row_gu[pos] = 2 * e;
-        a.suh_row_gu[a.n + pos] = 2 * e + 1;
+        const int rg = 2 * seg[e] + i, ru = rg + count[e];
+        a.row_src_gu[rg] = tok;
+        a.row_src_gu[ru] = tok;
+        a.suh_row_gu[rg] = 2 * e;
+        a.suh_row_gu[ru] = 2 * e + 1;
         a.suh_row_dn[pos] = e;
     }
     // tile tables: slot = row tile of one expert; every slot x every 256-column tile of the projection
@@ -165,25 +185,26 @@ __global__ void __launch_bounds__(1024) moe_prefill_tables_kernel(const MoePrefi
         reinterpret_cast<int4*>(tab)[2 * idx] = u;
         reinterpret_cast<int4*>(tab)[2 * idx + 1] = v;
     };
-    auto emit = [&](int slot, int e, int row0, int row_end) {
+    auto emit = [&](int slot, int e, int row0, int row_end, int gate_shift, int up_shift) {
         for (int j = 0; j < ct_h; j++) {
             const int nc = min(a.H - 256 * j, 256);
-            put(a.tiles_gu, slot * ct_h + j, row0, row_end, e * (a.H / 16) + 16 * j, e * 2 * a.H + 256 * j, 256 * j, nc, 0);
-            put(a.tiles_gu, (a.slots + slot) * ct_h + j, row0, row_end, (a.E + e) * (a.H / 16) + 16 * j,
-                e * 2 * a.H + a.H + 256 * j, a.H + 256 * j, nc, a.n);
+            put(a.tiles_gu, slot * ct_h + j, row0, row_end, e * (a.H / 16) + 16 * j, e * 2 * a.H + 256 * j, 256 * j, nc,
+                gate_shift);
+            put(a.tiles_gu, (a.slots + slot) * ct_h + j, row0, row_end, (E_here + e) * (a.H / 16) + 16 * j,
+                e * 2 * a.H + a.H + 256 * j, a.H + 256 * j, nc, up_shift);
         }
         for (int j = 0; j < ct_d; j++)
             put(a.tiles_dn, slot * ct_d + j, row0, row_end, e * (a.D / 16) + 16 * j, e * a.D + 256 * j, 256 * j,
                 min(a.D - 256 * j, 256), 0);
     };
-    for (int e = tid; e < a.E; e += blockDim.x) {
+    for (int e = tid; e < E_here; e += blockDim.x) {
         const int nb = (count[e] + 255) >> 8;
         for (int b = 0; b < nb; b++) {
             const int row0 = seg[e] + 256 * b;
-            emit(blk0[e] + b, e, row0, min(row0 + 256, seg[e] + count[e]));
+            emit(blk0[e] + b, e, row0, min(row0 + 256, seg[e] + count[e]), seg[e], seg[e] + count[e]);
         }
     }
-    for (int slot = total_blocks + tid; slot < a.slots; slot += blockDim.x) emit(slot, 0, 0, 0);   // unused
+    for (int slot = total_blocks + tid; slot < a.slots; slot += blockDim.x) emit(slot, 0, 0, 0, 0, 0);   // unused
 }
 
 }  // namespace exl3
@@ -236,26 +257,50 @@ extern "C" int exl3_moe_decode_tables_range(const void* indices, int index_bytes
                                   blocks_gu, row_src_gu, suh_row_gu, blocks_dn, suh_row_dn, counts, flags, stream);
 }
 
-extern "C" int exl3_moe_prefill_tables(const void* indices, int index_bytes, int n_pairs, int top_k,
-                                       int num_experts, int64_t d, int64_t h, int32_t* order,
-                                       int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* suh_row_dn,
-                                       int32_t* tiles_gu, int32_t* tiles_dn, unsigned flags,
-                                       exl3_stream_t stream)
+static int moe_prefill_tables_impl(const void* indices, int index_bytes, int n_pairs, int top_k, int num_experts,
+                                   int e_lo, int e_hi, int64_t d, int64_t h, int32_t* order, int32_t* row_src_gu,
+                                   int32_t* suh_row_gu, int32_t* suh_row_dn, int32_t* tiles_gu, int32_t* tiles_dn,
+                                   int32_t* counts, unsigned flags, exl3_stream_t stream)
 {
     if (!indices || !order || !row_src_gu || !suh_row_gu || !suh_row_dn || !tiles_gu || !tiles_dn)
         return EXL3_E_NULL;
     if (index_bytes != 4 && index_bytes != 8) return EXL3_E_DTYPE;
-    if (n_pairs < 1 || n_pairs > (1 << 20) || top_k < 1 || num_experts < 1 || num_experts > kMoeMaxExperts)
-        return EXL3_E_RANGE;
+    if (n_pairs < 1 || n_pairs > (1 << 20) || top_k < 1 || num_experts < 1) return EXL3_E_RANGE;
+    if (e_lo < 0 || e_hi <= e_lo || e_hi > num_experts || e_hi - e_lo > kMoeMaxExperts) return EXL3_E_RANGE;
     if (d < 128 || h < 128 || d % 128 || h % 128) return EXL3_E_SHAPE;
     if (((uintptr_t)tiles_gu | (uintptr_t)tiles_dn) & 15) return EXL3_E_ALIGN;
     MoePrefillArgs a;
     a.indices = indices;
     a.idx64 = index_bytes == 8;
     a.n = n_pairs; a.kk = top_k; a.E = num_experts; a.D = (int)d; a.H = (int)h;
-    a.slots = n_pairs / 256 + num_experts;
+    a.e_lo = e_lo; a.e_hi = e_hi;
+    a.slots = n_pairs / 256 + (e_hi - e_lo);
     a.order = order; a.row_src_gu = row_src_gu; a.suh_row_gu = suh_row_gu; a.suh_row_dn = suh_row_dn;
     a.tiles_gu = tiles_gu; a.tiles_dn = tiles_dn;
+    a.counts = counts;
     return launch_kernel(moe_prefill_tables_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream,
                          (flags & EXL3_FLAG_PDL) != 0, a);
+}
+
+extern "C" int exl3_moe_prefill_tables(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                       int num_experts, int64_t d, int64_t h, int32_t* order,
+                                       int32_t* row_src_gu, int32_t* suh_row_gu, int32_t* suh_row_dn,
+                                       int32_t* tiles_gu, int32_t* tiles_dn, unsigned flags,
+                                       exl3_stream_t stream)
+{
+    if (num_experts > kMoeMaxExperts) return EXL3_E_RANGE;
+    return moe_prefill_tables_impl(indices, index_bytes, n_pairs, top_k, num_experts, 0, num_experts, d, h, order,
+                                   row_src_gu, suh_row_gu, suh_row_dn, tiles_gu, tiles_dn, nullptr, flags, stream);
+}
+
+extern "C" int exl3_moe_prefill_tables_range(const void* indices, int index_bytes, int n_pairs, int top_k,
+                                             int num_experts, int expert_lo, int expert_hi, int64_t d, int64_t h,
+                                             int32_t* order, int32_t* row_src_gu, int32_t* suh_row_gu,
+                                             int32_t* suh_row_dn, int32_t* tiles_gu, int32_t* tiles_dn,
+                                             int32_t* counts, unsigned flags, exl3_stream_t stream)
+{
+    if (!counts) return EXL3_E_NULL;
+    return moe_prefill_tables_impl(indices, index_bytes, n_pairs, top_k, num_experts, expert_lo, expert_hi, d, h,
+                                   order, row_src_gu, suh_row_gu, suh_row_dn, tiles_gu, tiles_dn, counts, flags,
+                                   stream);
 }

@@ -135,50 +135,16 @@ class EXL3SwitchGLU(torch.nn.Module):
         return self._decode(x2d, indices, expert_range)
 
     # ---- prefill: pairs sorted by expert, tensor-core GEMM over an expert tile table ----------
-    @staticmethod
-    def _segments(sidx: torch.Tensor, E: int, n_pairs: int):
-        """Row tiles of <= 256 sorted pairs that never straddle two experts, built on the device
-        with a fixed upper bound of slots (the reference's block table, exl3_moe.py:79-99):
-        expert, first row and end row of every slot; unused slots have row0 == row_end."""
-        dev = sidx.device
-        mt = n_pairs // 256 + E
-        counts = torch.bincount(sidx, minlength=E)
-        nblk = (counts + 255) // 256
-        blk_end = torch.cumsum(nblk, 0)
-        slot = torch.arange(mt, device=dev)
-        blk_e = torch.clamp(torch.searchsorted(blk_end, slot, right=True), max=E - 1)
-        valid = slot < blk_end[-1]
-        seg_start = torch.cumsum(counts, 0) - counts
-        local = slot - (blk_end - nblk)[blk_e]
-        row0 = seg_start[blk_e] + local * 256
-        row_end = torch.minimum(row0 + 256, seg_start[blk_e] + counts[blk_e])
-        row0 = torch.where(valid, row0, torch.zeros_like(row0))
-        row_end = torch.where(valid, row_end, torch.zeros_like(row_end))
-        return blk_e.to(torch.int32), row0.to(torch.int32), row_end.to(torch.int32)
+    def _prefill(self, x2d: torch.Tensor, indices: torch.Tensor, expert_range=None, peers=None):
+        """Tables kernel, rotation + tile-table GEMM for gate and up, rotation (GLU applied while
+        loading) + tile-table GEMM for down writing straight back into (token, slot) order: five
+        launches, no host round trip.
 
-    @staticmethod
-    def _tiles(blk_e, row0, row_end, *, cols, tn_base, tiles_per_e, sv_base, sv_per_e, y_col0, row_shift):
-        """Tile table of one projection: every row tile x every 256-column tile of its expert."""
-        dev = blk_e.device
-        ct = (cols + 255) // 256
-        j = torch.arange(ct, device=dev, dtype=torch.int32).view(1, ct)
-        e = blk_e.view(-1, 1)
-        z = torch.zeros_like(e)
-        tab = torch.stack([
-            (row0.view(-1, 1) + row_shift) + z * j, (row_end.view(-1, 1) + row_shift) + z * j,
-            tn_base + e * tiles_per_e + 16 * j, sv_base + e * sv_per_e + 256 * j,
-            y_col0 + 256 * j + z, torch.clamp(cols - 256 * j, max=256) + z,
-            z * j - row_shift, z * j], dim=-1)
-        # slots that are unused must stay unused after the row shift
-        empty = (row0 >= row_end).view(-1, 1, 1)
-        tab = torch.where(empty & (torch.arange(8, device=dev).view(1, 1, 8) < 2), torch.zeros_like(tab), tab)
-        return tab.reshape(-1, 8).to(torch.int32).contiguous()
-
-    def _prefill(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
-        """Tables kernel, rotation + tile-table GEMM for gate and up, GLU, rotation + tile-table GEMM
-        for down writing straight back into (token, slot) order.  No host round trip."""
-        if self.activation != "silu":
-            return self._prefill_torch_tables(x2d, indices)
+        expert_range = (lo, hi, total) and peers = (y_ptrs, counter_ptrs, n, rows_per_peer,
+        row_stride): expert parallelism — this module holds experts lo..hi-1, `indices` are global
+        and cover ALL tokens; only the held pairs are computed (their number stays on the device)
+        and every output row is stored into the memory of the GPU that owns its token, which
+        gets one arrival per GPU when the rows are complete (exl3_gemm_tiles_peers)."""
         from . import _lib
         E, D, H = self.num_experts, self.input_dims, self.hidden_dims
         R, kk = indices.shape
@@ -191,55 +157,44 @@ class EXL3SwitchGLU(torch.nn.Module):
         slots = n // 256 + E
         ct_h, ct_d = (H + 255) // 256, (D + 255) // 256
         n_gu, n_dn = 2 * slots * ct_h * 8, slots * ct_d * 8
-        tab = torch.empty(n_gu + n_dn + 6 * n, dtype=torch.int32, device=dev)   # tiles first: 16-byte aligned
+        tab = torch.empty(n_gu + n_dn + 6 * n + 4, dtype=torch.int32, device=dev)   # tiles first: 16-byte aligned
         tiles_gu, tiles_dn = tab[:n_gu].view(-1, 8), tab[n_gu:n_gu + n_dn].view(-1, 8)
         o = n_gu + n_dn
         order, row_src = tab[o:o + n], tab[o + n:o + 3 * n]
         suh_gu, suh_dn = tab[o + 3 * n:o + 5 * n], tab[o + 5 * n:o + 6 * n]
-        _lib.check(_lib.load().exl3_moe_prefill_tables(
-            idx.data_ptr(), idx.element_size(), n, kk, E, D, H, order.data_ptr(), row_src.data_ptr(),
-            suh_gu.data_ptr(), suh_dn.data_ptr(), tiles_gu.data_ptr(), tiles_dn.data_ptr(), 0,
-            torch.cuda.current_stream(dev).cuda_stream), "exl3_moe_prefill_tables")
+        counts = tab[o + 6 * n:o + 6 * n + 2]
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        if expert_range is None:
+            _lib.check(_lib.load().exl3_moe_prefill_tables(
+                idx.data_ptr(), idx.element_size(), n, kk, E, D, H, order.data_ptr(), row_src.data_ptr(),
+                suh_gu.data_ptr(), suh_dn.data_ptr(), tiles_gu.data_ptr(), tiles_dn.data_ptr(), 0, stream),
+                "exl3_moe_prefill_tables")
+            rows_gu = rows_dn = None
+        else:
+            lo, hi, total = expert_range
+            if hi - lo != E:
+                raise ValueError("expert_range does not match the experts held here")
+            _lib.check(_lib.load().exl3_moe_prefill_tables_range(
+                idx.data_ptr(), idx.element_size(), n, kk, total, lo, hi, D, H, order.data_ptr(), row_src.data_ptr(),
+                suh_gu.data_ptr(), suh_dn.data_ptr(), tiles_gu.data_ptr(), tiles_dn.data_ptr(), counts.data_ptr(),
+                0, stream), "exl3_moe_prefill_tables_range")
+            rows_gu, rows_dn = counts[0:1], counts[1:2]
         ygu = torch.empty((n, 2 * H), dtype=torch.float16, device=dev)
         ops.gemm_tiles(x2d, xh_rows=2 * n, row_src=row_src, suh=self._gu_suh, suh_row=suh_gu,
-                       trellis=self._gu_trellis, k=self.k, cb=self.cb, tiles=tiles_gu, svh=self._gu_svh, y=ygu)
-        h = ops.swiglu(ygu)
-        out = torch.empty((n, D), dtype=torch.float16, device=dev)
-        ops.gemm_tiles(h, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=suh_dn, trellis=self._dn_trellis,
-                       k=self.k, cb=self.cb, tiles=tiles_dn, svh=self._dn_svh, y=out, y_row_map=order)
-        return out.view(R, kk, D)
+                       trellis=self._gu_trellis, k=self.k, cb=self.cb, tiles=tiles_gu, svh=self._gu_svh, y=ygu,
+                       xh_rows_dev=rows_gu)
+        # the down launch reads [gate | up] as it is and applies the GLU while it rotates the rows
+        out = None if peers is not None else torch.empty((n, D), dtype=torch.float16, device=dev)
+        ops.gemm_tiles(ygu, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=suh_dn, trellis=self._dn_trellis,
+                       k=self.k, cb=self.cb, tiles=tiles_dn, svh=self._dn_svh, y=out, y_row_map=order,
+                       glu=self.activation, xh_rows_dev=rows_dn, peers=peers)
+        return None if out is None else out.view(R, kk, D)
 
-    def _prefill_torch_tables(self, x2d: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
-        E, D, H = self.num_experts, self.input_dims, self.hidden_dims
-        R, kk = indices.shape
-        n = R * kk
-        dev = x2d.device
-        flat = indices.reshape(-1).to(torch.int64)
-        order = torch.argsort(flat, stable=True)
-        sidx = flat[order]
-        tok = torch.div(order, kk, rounding_mode="floor").to(torch.int32)
-        blk_e, row0, row_end = self._segments(sidx, E, n)
-        s32 = sidx.to(torch.int32)
-
-        # gate and up in one launch: rotated rows [0, n) use the gate signs, [n, 2n) the up signs
-        t_g = self._tiles(blk_e, row0, row_end, cols=H, tn_base=0, tiles_per_e=H // 16, sv_base=0,
-                          sv_per_e=2 * H, y_col0=0, row_shift=0)
-        t_u = self._tiles(blk_e, row0, row_end, cols=H, tn_base=E * (H // 16), tiles_per_e=H // 16,
-                          sv_base=H, sv_per_e=2 * H, y_col0=H, row_shift=n)
-        ygu = torch.empty((n, 2 * H), dtype=torch.float16, device=dev)
-        ops.gemm_tiles(x2d, xh_rows=2 * n, row_src=torch.cat([tok, tok]).contiguous(), suh=self._gu_suh,
-                       suh_row=torch.cat([2 * s32, 2 * s32 + 1]).contiguous(), trellis=self._gu_trellis,
-                       k=self.k, cb=self.cb, tiles=torch.cat([t_g, t_u]), svh=self._gu_svh, y=ygu)
-        h = glu(ygu[:, :H], ygu[:, H:], self.activation)
-
-        t_d = self._tiles(blk_e, row0, row_end, cols=D, tn_base=0, tiles_per_e=D // 16, sv_base=0,
-                          sv_per_e=D, y_col0=0, row_shift=0)
-        out = torch.empty((n, D), dtype=torch.float16, device=dev)
-        ops.gemm_tiles(h, xh_rows=n, row_src=None, suh=self._dn_suh, suh_row=s32.contiguous(),
-                       trellis=self._dn_trellis, k=self.k, cb=self.cb, tiles=t_d, svh=self._dn_svh, y=out)
-        inv = torch.empty_like(order)
-        inv[order] = torch.arange(n, device=dev)
-        return out[inv].view(R, kk, D)
+    @torch.no_grad()
+    def prefill_range(self, x2d: torch.Tensor, indices: torch.Tensor, expert_range, peers) -> None:
+        """Expert parallelism, many tokens: see _prefill.  x2d (T, D) and indices (T, k) cover all
+        tokens; the outputs land in the owners' buffers named by `peers`."""
+        self._prefill(x2d, indices, expert_range, peers)
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:

@@ -282,13 +282,18 @@ def gemv_blocks(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None
 
 def gemm_tiles(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None,
                suh: torch.Tensor | None, suh_row: torch.Tensor | None, trellis: torch.Tensor, k: int,
-               cb: int, tiles: torch.Tensor, svh: torch.Tensor | None, y: torch.Tensor,
-               y_row_map: torch.Tensor | None = None) -> torch.Tensor:
+               cb: int, tiles: torch.Tensor, svh: torch.Tensor | None, y: torch.Tensor | None,
+               y_row_map: torch.Tensor | None = None, glu: str | None = None,
+               xh_rows_dev: torch.Tensor | None = None, peers=None) -> torch.Tensor | None:
     """Tensor-core GEMM over a tile table (see exl3_gemm_tiles in the header).  `tiles` is an
-    int32 CUDA tensor (n_tiles, 8); `y` (rows, cols) fp16 is written in place."""
+    int32 CUDA tensor (n_tiles, 8); `y` (rows, cols) fp16 is written in place.
+    glu: x2d rows are [gate | up] and the input is fp16(act(gate) * up).
+    xh_rows_dev: int32 CUDA scalar, rotated rows in use.  peers = (y_ptrs, counter_ptrs, n,
+    rows_per_peer, row_stride): the output rows go to the GPUs that own them (y may be None), see
+    exl3_gemm_tiles_peers."""
     _need_cuda(x2d, "x")
     t_in, t_out_total, _ = trellis.shape
-    if x2d.shape[1] != t_in * 16:
+    if x2d.shape[1] != t_in * 16 * (2 if glu is not None else 1):
         raise ValueError(f"x has {x2d.shape[1]} features, layer expects {t_in * 16}")
     if tiles.dtype != torch.int32 or tiles.ndim != 2 or tiles.shape[1] != 8:
         raise ValueError("tiles must be an int32 tensor of shape (n_tiles, 8)")
@@ -298,11 +303,23 @@ def gemm_tiles(x2d: torch.Tensor, *, xh_rows: int, row_src: torch.Tensor | None,
     lib = _lib.load()
     ws = Workspace.get_bytes(x2d.device, int(lib.exl3_gemm_workspace_bytes(xh_rows, t_in * 16)))
     ptr = lambda t: None if t is None else t.data_ptr()
-    _lib.check(lib.exl3_gemm_tiles(
-        x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),
-        ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), tiles.data_ptr(),
-        tiles.shape[0], ptr(svh), y.data_ptr(), y.stride(0), ptr(y_row_map), ws.buf.data_ptr(), ws.nbytes, 0,
-        _stream(x2d.device)), "exl3_gemm_tiles")
+    flags = _GLU_FLAGS[glu]
+    if peers is None and xh_rows_dev is None:
+        _lib.check(lib.exl3_gemm_tiles(
+            x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(row_src), ptr(suh),
+            ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), tiles.data_ptr(),
+            tiles.shape[0], ptr(svh), y.data_ptr(), y.stride(0), ptr(y_row_map), ws.buf.data_ptr(), ws.nbytes, flags,
+            _stream(x2d.device)), "exl3_gemm_tiles")
+        return y
+    if peers is None:
+        y_ptrs, c_ptrs, n_peers, rows_per_peer, stride = None, None, 0, 0, y.stride(0)
+    else:
+        y_ptrs, c_ptrs, n_peers, rows_per_peer, stride = peers
+    _lib.check(lib.exl3_gemm_tiles_peers(
+        x2d.data_ptr(), _DTYPES[x2d.dtype], x2d.stride(0), xh_rows, ptr(xh_rows_dev), ptr(row_src), ptr(suh),
+        ptr(suh_row), trellis.data_ptr(), t_in, t_out_total, k, int(cb), tiles.data_ptr(), tiles.shape[0],
+        ptr(svh), ptr(y), stride, ptr(y_row_map), y_ptrs, c_ptrs, n_peers, rows_per_peer, ws.buf.data_ptr(),
+        ws.nbytes, flags, _stream(x2d.device)), "exl3_gemm_tiles_peers")
     return y
 
 

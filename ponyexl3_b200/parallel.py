@@ -112,8 +112,9 @@ def shard_expert_weights(w: dict, num_experts: int, world: int, rank: int) -> di
 
 class EPSwitchGLU(torch.nn.Module):
     """Stacked experts sharded by expert.  `local(x (1,T,D), idx (1,T,k)) -> (1,T,k,D)` is this
-    rank's switch over its own experts (local indices); tokens are replicated on every rank.
-    Pairs routed to another rank's expert are computed there; the partial outputs are summed."""
+    rank's switch over its own experts (local indices).  `forward`: tokens replicated on every
+    rank, pairs routed to another rank's expert are computed there, the partial outputs are
+    summed.  `forward_partitioned`: many tokens, partitioned over the ranks."""
 
     def __init__(self, local: Callable, num_experts: int, group=None):
         super().__init__()
@@ -153,6 +154,39 @@ class EPSwitchGLU(torch.nn.Module):
         else:
             dist.all_reduce(out, group=self.group)
         return out.reshape(B, S, kk, D)
+
+
+    def forward_partitioned(self, x_local: torch.Tensor, idx_local: torch.Tensor) -> torch.Tensor:
+        """Many tokens, partitioned over the ranks (T_local each, the same on every rank): all
+        ranks gather the tokens and their routing (NCCL all-gather), every rank runs its experts
+        over the pairs routed to them — picked and counted on the device — and its down
+        projection stores each output row straight into the memory of the rank that owns the
+        token (peer stores over NVLink, `exl3_gemm_tiles_peers`).  Returns this rank's
+        (T_local, k, D) outputs, a view of an exchange buffer that the next call but two reuses.
+        No value ever reaches the host, so the call can be captured in a CUDA graph (the exchange
+        buffers rotate per call: a replayed graph must not run twice in a row, see PeerExchange)."""
+        from . import _lib, ops
+
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        e0, e1 = shard_experts(self.num_experts, world, rank)
+        T, kk = idx_local.shape
+        D = x_local.shape[-1]
+        n_local = T * kk
+        ex = self.__dict__.get("_exchange")
+        if ex is None or ex.max_rows < n_local or ex.max_cols != D:
+            ex = PeerExchange(n_local, D, self.group, ring=3)
+            self.__dict__["_exchange"] = ex
+        x_all = torch.empty((world * T, D), dtype=x_local.dtype, device=x_local.device)
+        dist.all_gather_into_tensor(x_all, x_local.contiguous(), group=self.group)
+        idx_all = torch.empty((world * T, kk), dtype=idx_local.dtype, device=idx_local.device)
+        dist.all_gather_into_tensor(idx_all, idx_local.contiguous(), group=self.group)
+        _, y_ptrs, c_ptrs, view, my_ctr = ex.take(n_local, D)
+        self.local.prefill_range(x_all, idx_all, (e0, e1, self.num_experts), (y_ptrs, c_ptrs, world, n_local, D))
+        dev = x_local.device
+        ws = ops.Workspace.get(dev, 1, 128)
+        _lib.check(_lib.load().exl3_peer_wait(my_ctr, world, ws.buf.data_ptr(), 0,
+                                              torch.cuda.current_stream(dev).cuda_stream), "exl3_peer_wait")
+        return view.view(T, kk, D)
 
 
 def dispatch_rows_to_experts(x_local: torch.Tensor, idx_local: torch.Tensor, num_experts: int, group=None):

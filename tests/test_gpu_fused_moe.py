@@ -237,6 +237,45 @@ def test_decode_over_an_expert_range_sums_to_the_full_switch(cuda, oracle, world
     assert rel_err(total.cpu().numpy(), want) <= 2e-3
 
 
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+def test_prefill_over_an_expert_range_stores_rows_at_their_owners(cuda, oracle, world, act):
+    """Expert parallelism for many tokens, every rank's share computed one after the other on
+    this GPU: tokens are partitioned (buffer p holds the output rows of partition p), a rank
+    sorts and tiles only the pairs of its experts (their number stays on the device), its down
+    projection stores each row into the owner's buffer and announces itself on every owner's
+    counter.  After all ranks every counter holds `world` arrivals and the buffers hold the
+    oracle's output."""
+    import ctypes
+
+    from ponyexl3_b200 import ops
+    from ponyexl3_b200.parallel import shard_expert_weights, shard_experts
+
+    E, D, H, kk, k, T = 16, 256, 128, 4, 4, 96
+    w = _experts(E, D, H, k, seed=930 + world)
+    rng = np.random.default_rng(31 + world)
+    x = (rng.standard_normal((T, D)) * 0.5).astype(np.float16)
+    idx = np.stack([rng.choice(E, size=kk, replace=False) for _ in range(T)]).astype(np.int64)
+    xd, idd = torch.from_numpy(x).cuda(), torch.from_numpy(idx).cuda()
+    n_local = T // world * kk
+    bufs = [torch.full((n_local, D), float("nan"), dtype=torch.float16, device="cuda") for _ in range(world)]
+    ctrs = torch.zeros(world * 64, dtype=torch.int32, device="cuda")      # counters 256 bytes apart
+    u64 = ctypes.c_uint64 * world
+    y_ptrs = u64(*[b.data_ptr() for b in bufs])
+    c_ptrs = u64(*[ctrs.data_ptr() + 256 * p for p in range(world)])
+    for rank in range(world):
+        e0, e1 = shard_experts(E, world, rank)
+        sw = _switch(shard_expert_weights(w, E, world, rank), k, 0, act)
+        sw.prefill_range(xd, idd, (e0, e1, E), (y_ptrs, c_ptrs, world, n_local, D))
+    torch.cuda.synchronize()
+    assert ctrs.view(world, 64)[:, 0].tolist() == [world] * world
+    assert ops.Workspace.get(torch.device("cuda"), 1, 128).status() == 0
+    got = torch.cat(bufs).cpu().numpy().reshape(T, kk, D)
+    assert np.isfinite(got.astype(np.float32)).all()          # every row was written by somebody
+    want = oracle.switch_glu(x, idx, **w, k=k, cb=0, activation=act)
+    assert rel_err(got, want) <= 2e-3
+
+
 @pytest.mark.parametrize("act", ["silu", "gelu"])
 @pytest.mark.parametrize("rows", [1, 3, 8, 16])
 def test_glu_folded_into_the_down_projection(cuda, oracle, act, rows):

@@ -90,6 +90,20 @@ def _expert_parallel(rank, world):
         yr = torch.empty((0, D), dtype=torch.float16, device=dev)
     back = return_rows_to_tokens(yr, book)
     assert torch.equal(back, want[t0:t1]), f"rank {rank}: expert-parallel exchange path"
+    # many tokens, partitioned: gathered tokens, pairs picked on the device, rows stored into the
+    # owner's memory over the peer mapping; twice, so that the exchange buffers rotate
+    T2 = 64
+    x2 = (torch.randn((T2, D), device=dev, generator=g) * 0.5).to(torch.float16)
+    idx2 = torch.stack([torch.randperm(E, device=dev, generator=g)[:kk] for _ in range(T2)])
+    want2 = full(x2.view(1, T2, D), idx2.view(1, T2, kk)).reshape(T2, kk, D)
+    a0, a1 = T2 * rank // world, T2 * (rank + 1) // world
+    ep = EPSwitchGLU(local, E)
+    for rep in range(2):
+        got2 = ep.forward_partitioned(x2[a0:a1].contiguous(), idx2[a0:a1].contiguous())
+        torch.cuda.synchronize()
+        assert torch.equal(got2, want2[a0:a1]), f"rank {rank}: expert-parallel partitioned path, call {rep}"
+    from ponyexl3_b200 import ops
+    assert ops.Workspace.get(dev, 1, 128).status() == 0
 
 
 def _dense_step(rank, world):
