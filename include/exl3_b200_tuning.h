@@ -22,7 +22,8 @@ extern "C" {
 EXL3_API void exl3_tune_gemv(int max_grid, int fuse_x_bytes);
 
 /* one_acc_rows: 128 (default) = an output tile of the prefill GEMM with at most 128 rows loads,
- * multiplies and drains only its first accumulator; 0 = every tile uses both (for comparison). */
+ * multiplies and drains only its first accumulator; 0 = every tile uses both (for comparison).
+ * + 256: a dense layer's short last wave of tiles is NOT cut into 128-column half tiles. */
 EXL3_API void exl3_tune_gemm(int one_acc_rows);
 
 /* on: 1 = dense prefill GEMMs of 1024 rows and more run on pairs of SMs

@@ -5,7 +5,12 @@
 namespace exl3 {
 
 int g_gemm_one_acc_rows = 128;
-void gemm_set_tuning(int one_acc_rows) { g_gemm_one_acc_rows = one_acc_rows == 0 ? 0 : 128; }
+int g_gemm_split_last_wave = 1;
+void gemm_set_tuning(int one_acc_rows)
+{
+    g_gemm_one_acc_rows = (one_acc_rows & 255) == 0 ? 0 : 128;
+    g_gemm_split_last_wave = (one_acc_rows & 256) ? 0 : 1;     // + 256: whole tiles only
+}
 // Off: measured on 8192 x 5120 x 5120 the pair kernel is at 0.43 ms against 0.40 ms (see exl3_gemm2.cuh).
 int g_gemm_pairs = 0;
 void gemm_set_pairs(int on) { g_gemm_pairs = on ? 1 : 0; }

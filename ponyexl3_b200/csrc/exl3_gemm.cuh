@@ -83,24 +83,38 @@ __device__ __forceinline__ void had128_regs(float (&v)[128])
 // slot that every role skips.
 struct GemmTile {
     int m0, m_end, tn0, sv_off, y_col, ncols, y_row_delta;
+    int half;      // -1: all 256 columns; 0 / 1: only the first / second 128 columns of the packed box
 };
-__device__ __forceinline__ GemmTile gemm_tile(const GemmArgs& a, int tile)
+// Dense layers: the first a.n_full_tiles work items are whole tiles; the tiles that would make up
+// a short last wave are cut into two 128-column halves each (half the decode, half the MMAs), so
+// that the last wave keeps more SMs busy for half as long.
+__device__ __forceinline__ GemmTile gemm_tile(const GemmArgs& a, int item)
 {
     GemmTile t;
     if (a.tile_tab) {
-        const int4 u = reinterpret_cast<const int4*>(a.tile_tab)[2 * tile];
-        const int4 v = reinterpret_cast<const int4*>(a.tile_tab)[2 * tile + 1];
+        const int4 u = reinterpret_cast<const int4*>(a.tile_tab)[2 * item];
+        const int4 v = reinterpret_cast<const int4*>(a.tile_tab)[2 * item + 1];
         t.m0 = u.x; t.m_end = u.y; t.tn0 = u.z; t.sv_off = u.w;
         t.y_col = v.x; t.ncols = v.y; t.y_row_delta = v.z;
+        t.half = -1;
     } else {
+        int tile = item, h = -1;
+        if (item >= a.n_full_tiles) {
+            const int j = item - a.n_full_tiles;
+            tile = a.n_full_tiles + (j >> 1);
+            h = j & 1;
+        }
         const int n0 = (tile % a.tiles_n) * kTileN;
         t.m0 = (tile / a.tiles_n) * kTileM;
         t.m_end = a.m;
         t.tn0 = n0 / 16;
-        t.sv_off = n0;
-        t.y_col = n0;
-        t.ncols = a.t_out * 16 - n0;
+        t.half = h;
+        const int c0 = n0 + (h > 0 ? 128 : 0);
+        t.sv_off = c0;
+        t.y_col = c0;
+        t.ncols = h < 0 ? a.t_out * 16 - n0 : min(128, a.t_out * 16 - c0);
         t.y_row_delta = 0;
+        if (t.ncols <= 0) t.m_end = t.m0;      // a second half beyond the last column: nothing to do
     }
     return t;
 }
@@ -123,7 +137,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nks = a.t_in / 4;                                // 64-wide k-steps
-    const int n_tiles = a.tile_tab ? a.n_tiles_tab : a.tiles_m * a.tiles_n;
+    const int n_tiles = a.n_items;                             // work items: tiles, or tiles and half tiles
 
     if (tid == 0) {
         for (int s = 0; s < NS; s++) {
@@ -172,16 +186,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     } else if (warp == 1) {
         // -------------------------------------------------------------------- MMA issuer ----
         if (lane == 0) {
-            constexpr uint32_t idesc = mma_idesc_f16(128, kTileN);
             int s = 0;
             uint32_t parity = 0, tile_parity = 0;
             bool first_tile = true;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
                 bool two;
+                uint32_t idesc;
                 {
                     const GemmTile ti = gemm_tile(a, tile);
                     if (ti.m0 >= ti.m_end) continue;
                     two = ti.m_end - ti.m0 > a.one_acc_rows;
+                    idesc = ti.half < 0 ? mma_idesc_f16(128, kTileN) : mma_idesc_f16(128, 128);
                 }
                 if (!first_tile) {   // the epilogue of the previous tile must have drained D
                     if (!mbar_wait(smem_u32(tmem_empty), tile_parity ^ 1u)) {
@@ -241,33 +256,43 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 // All packed words of the warp's eight tiles are fetched before the first store: the
                 // stores into the B tile could alias the packed words as far as the compiler knows,
                 // so loads written after them would wait for them, tile after tile.
+                // Whole tile: this warp decodes tile columns 2 dw, 2 dw + 1 of all four tile rows; half
+                // tile: column 8 half + dw of the box, stored as column dw of a 128-column B tile.
+                const int n_mine = ti.half < 0 ? 8 : 4;
                 uint32_t pw[8][3];
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const uint32_t* tw = wt + ((i >> 1) * 16 + 2 * dw + (i & 1)) * L::kTileWords;
-                    if (K == 4) {
-                        pw[i][0] = tw[lane];
-                        pw[i][1] = tw[prev_word];
-                        pw[i][2] = 0u;
-                    } else {
-                        pw[i][0] = tw[lw.i0];
-                        pw[i][1] = tw[lw.i1];
-                        pw[i][2] = LaneWords<K>::kThree ? tw[lw.i2] : 0u;
+                    if (i < n_mine) {
+                        const int tk = ti.half < 0 ? i >> 1 : i;
+                        const int tn = ti.half < 0 ? 2 * dw + (i & 1) : 8 * ti.half + dw;
+                        const uint32_t* tw = wt + (tk * 16 + tn) * L::kTileWords;
+                        if (K == 4) {
+                            pw[i][0] = tw[lane];
+                            pw[i][1] = tw[prev_word];
+                            pw[i][2] = 0u;
+                        } else {
+                            pw[i][0] = tw[lw.i0];
+                            pw[i][1] = tw[lw.i1];
+                            pw[i][2] = LaneWords<K>::kThree ? tw[lw.i2] : 0u;
+                        }
                     }
                 }
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const int tk = i >> 1, tn = 2 * dw + (i & 1);
-                    uint32_t cw[8];
-                    if (K == 4) lane_codewords_k4(pw[i][0], pw[i][1], cw);
-                    else lane_codewords<K>(pw[i][0], pw[i][1], pw[i][2], lw.sh, cw);
-                    // B[n][k] K-major, 128B swizzle: n = 16 tn + g (+8), k = 16 tk + 2q (+8)
-                    uint8_t* row = bt + (2 * tn) * 1024 + g * 128 + 4 * q;
-                    const int c0 = ((2 * tk) ^ g) << 4, c1 = ((2 * tk + 1) ^ g) << 4;
-                    *reinterpret_cast<uint32_t*>(row + c0) = decode_pair_rt<CB>(cw[0], cw[1], xc);
-                    *reinterpret_cast<uint32_t*>(row + 1024 + c0) = decode_pair_rt<CB>(cw[4], cw[5], xc);
-                    *reinterpret_cast<uint32_t*>(row + c1) = decode_pair_rt<CB>(cw[2], cw[3], xc);
-                    *reinterpret_cast<uint32_t*>(row + 1024 + c1) = decode_pair_rt<CB>(cw[6], cw[7], xc);
+                    if (i < n_mine) {
+                        const int tk = ti.half < 0 ? i >> 1 : i;
+                        const int tn = ti.half < 0 ? 2 * dw + (i & 1) : dw;
+                        uint32_t cw[8];
+                        if (K == 4) lane_codewords_k4(pw[i][0], pw[i][1], cw);
+                        else lane_codewords<K>(pw[i][0], pw[i][1], pw[i][2], lw.sh, cw);
+                        // B[n][k] K-major, 128B swizzle: n = 16 tn + g (+8), k = 16 tk + 2q (+8)
+                        uint8_t* row = bt + (2 * tn) * 1024 + g * 128 + 4 * q;
+                        const int c0 = ((2 * tk) ^ g) << 4, c1 = ((2 * tk + 1) ^ g) << 4;
+                        *reinterpret_cast<uint32_t*>(row + c0) = decode_pair_rt<CB>(cw[0], cw[1], xc);
+                        *reinterpret_cast<uint32_t*>(row + 1024 + c0) = decode_pair_rt<CB>(cw[4], cw[5], xc);
+                        *reinterpret_cast<uint32_t*>(row + c1) = decode_pair_rt<CB>(cw[2], cw[3], xc);
+                        *reinterpret_cast<uint32_t*>(row + 1024 + c1) = decode_pair_rt<CB>(cw[6], cw[7], xc);
+                    }
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -371,6 +396,7 @@ done:
 // ---- host side ----------------------------------------------------------------------------------
 
 extern int g_gemm_one_acc_rows;   // exl3_gemm.cu: 128, or 0 from the benchmark hook (always two accumulators)
+extern int g_gemm_split_last_wave;   // exl3_gemm.cu: 1, or 0 from the benchmark hook
 
 template <int K, int CB>
 static int launch_gemm_t(GemmArgs a, const __half* xh, const uint32_t* trellis, cudaStream_t s)
@@ -406,7 +432,16 @@ static int launch_gemm_t(GemmArgs a, const __half* xh, const uint32_t* trellis, 
     a.tiles_n = (a.t_out * 16 + kTileN - 1) / kTileN;
     a.cb_xor = 0x3B603B60u;
     a.one_acc_rows = g_gemm_one_acc_rows;
-    const int grid = std::min(a.tile_tab ? a.n_tiles_tab : a.tiles_m * a.tiles_n, device_sm_count());
+    const int sms = device_sm_count();
+    if (a.tile_tab) {
+        a.n_full_tiles = a.n_items = a.n_tiles_tab;
+    } else {
+        // a last wave that would fill at most half of the SMs is run as half tiles
+        const int n = a.tiles_m * a.tiles_n, rest = n % sms;
+        a.n_full_tiles = (n > sms && rest > 0 && 2 * rest <= sms && g_gemm_split_last_wave) ? n - rest : n;
+        a.n_items = a.n_full_tiles + 2 * (n - a.n_full_tiles);
+    }
+    const int grid = std::min(a.n_items, sms);
     gemm_kernel<K, CB><<<grid, kGemmThreads, L::kSmemBytes, s>>>(a, tm_x, tm_w);
     return check_launch();
 }

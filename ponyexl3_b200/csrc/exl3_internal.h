@@ -164,6 +164,7 @@ struct GemmArgs {
     int m;                    // rows (tokens)
     int t_in, t_out;          // tiles
     int tiles_m, tiles_n;
+    int n_full_tiles, n_items; // dense: whole tiles, then two half tiles per remaining tile (see gemm_tile)
     int stages;
     int one_acc_rows;         // tiles with at most this many rows use only the first accumulator
     uint32_t cb_xor;
