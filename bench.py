@@ -38,7 +38,7 @@ UNIT = "GB/s"
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum over packed weight bytes, from the ncu capture of
 # the K=4 batch-1 GEMV 5120 -> 17408
-DRAM_TRAFFIC_RATIO = 1.0027
+DRAM_TRAFFIC_RATIO = 1.0028
 
 
 def packed_bytes(shape, k=K_BITS):
@@ -527,11 +527,11 @@ def run_gpu(args):
                 "bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                 "frac": per_gpu / peak, "traffic": DRAM_TRAFFIC_RATIO * step_bytes_global / world / n_gemv,
                 "traffic_unit": "bytes per launch (dram read + write)",
-                "traffic_note": "ncu capture of the 5120x17408 launch: 44.68 MB read + 2.3 KB written for "
-                                "44.56 MB of packed weights (ratio 1.0027); scaled by packed bytes to the "
+                "traffic_note": "ncu capture of the 5120x17408 launch: 44.69 MB read + 2.6-8.4 KB written for "
+                                "44.56 MB of packed weights (ratio 1.0028); scaled by packed bytes to the "
                                 "average launch of this step",
                 "peak_kind": f"of {peak_kind}",
-                "kernel": "exl3::gemv_kernel<4,0,1>",
+                "kernel": "exl3::gemv_kernel<4,0,1,0,1>",
                 "note": "achieved = packed bytes per launch / (step time / GEMV launches); both "
                         "rotations run inside the GEMV kernel",
                 "avg_launch_us": 1e3 * ms / args.steps / n_gemv,
