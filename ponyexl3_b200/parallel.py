@@ -10,9 +10,12 @@ equals the unsharded one.
   per-rank outputs are all-gathered (NCCL on GPUs, gloo in the CPU tests).
 * Stacked MoE experts — expert parallel: rank g owns a contiguous range of experts (a
   contiguous out-tile range of the stacked trellises).  Decode-class calls replicate the few
-  tokens, every rank computes the (token, slot) pairs whose expert it owns and the partial
-  outputs are summed (all-reduce); prefill-class calls with tokens partitioned over the ranks
-  exchange rows with two all-to-alls.
+  tokens, every rank computes the (token, slot) pairs whose expert it owns — picked and counted
+  on the device — and the partial outputs are summed (all-reduce).  Prefill-class calls with
+  tokens partitioned over the ranks gather tokens and routing, every rank computes the pairs of
+  its experts and stores each output row into the memory of the rank that owns the token
+  (``EPSwitchGLU.forward_partitioned``); the same exchange written as two all-to-alls
+  (``dispatch_rows_to_experts`` / ``return_rows_to_tokens``) is what the CPU tests run.
 """
 
 from __future__ import annotations
