@@ -588,12 +588,17 @@ static int gemm_tiles_impl(const void* x, int x_dtype, int64_t x_row_stride, int
     a.n_peer = peers.n;
     a.rows_per_peer = (int)peers.rows_per_peer;
     a.done_ctr = reinterpret_cast<unsigned*>(ws + kWsDoneCtr);
+    bool wide = y_row_stride % 16 == 0 && (peers.n > 0 || aligned(y, 32));
     for (int p = 0; p < peers.n; p++) {
         if (!peers.y[p] || !peers.ctr[p]) return EXL3_E_NULL;
         if (peers.y[p] % 16 || peers.ctr[p] % 4) return EXL3_E_ALIGN;
+        wide = wide && peers.y[p] % 32 == 0;
         a.y_peer[p] = reinterpret_cast<__half*>(peers.y[p]);
         a.ctr_peer[p] = reinterpret_cast<unsigned*>(peers.ctr[p]);
     }
+    // tile tables place outputs at multiples of 128 columns, so a 32-byte aligned base and row
+    // stride make every 16-column piece 32-byte aligned
+    a.y_wide = wide ? 1 : 0;
     return launch_gemm(a, k, cb, xh, reinterpret_cast<const uint32_t*>(trellis), s);
 }
 

@@ -61,6 +61,14 @@ template <int CB> __device__ __forceinline__ uint32_t decode_pair_rt(uint32_t cw
     return h2_as_u32(__hadd2(u32_as_h2(lo), u32_as_h2(hi)));
 }
 
+// One 32-byte store (sm_100: 256-bit vector stores); p must be 32-byte aligned.
+__device__ __forceinline__ void st_global_256(void* p, const uint4& a, const uint4& b)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+                 "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
 // In-register 128-point Sylvester Hadamard (un-normalised).
 __device__ __forceinline__ void had128_regs(float (&v)[128])
 {
@@ -333,6 +341,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         } else {
                             yp = a.y + (int64_t)orow * a.y_row_stride + col0;
                         }
+                        uint4 held = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
                         for (int c = 0; c < 16; c++) {
                             float o[8];
@@ -360,7 +369,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                             uint4 ov;
                             ov.x = h2_as_u32(h[0]); ov.y = h2_as_u32(h[1]);
                             ov.z = h2_as_u32(h[2]); ov.w = h2_as_u32(h[3]);
-                            *reinterpret_cast<uint4*>(yp + 8 * c) = ov;
+                            if (!a.y_wide) {
+                                *reinterpret_cast<uint4*>(yp + 8 * c) = ov;
+                            } else if (c & 1) {
+                                // 32-byte stores (whole sectors): what a row stored into another GPU's
+                                // memory travels as
+                                st_global_256(yp + 8 * (c - 1), held, ov);
+                            } else {
+                                held = ov;
+                            }
                         }
                     }
                 }

@@ -176,6 +176,7 @@ struct GemmArgs {
     __half* y_peer[kMaxPeers];
     unsigned* ctr_peer[kMaxPeers];
     unsigned* done_ctr;       // local: CTAs that have stored all their tiles
+    int y_wide;               // every output row piece is 32-byte aligned: store 32 bytes at a time
 };
 
 int launch_gemm(const GemmArgs& a, int k, int cb, const __half* xh, const uint32_t* trellis,
