@@ -525,6 +525,7 @@ int exl3_gemm(const void* x, int x_dtype, int64_t rows, int64_t x_row_stride, co
     a.xh_rows = (int)rows;
     a.t_in = (int)t_in;
     a.t_out = (int)t_out;
+    a.y_wide = (y_row_stride % 16 == 0 && aligned(y, 32)) ? 1 : 0;   // 32-byte stores in the epilogue
     return launch_gemm(a, k, cb, xh, reinterpret_cast<const uint32_t*>(trellis), s);
 }
 
