@@ -73,6 +73,29 @@ def test_host_side_validation_needs_no_gpu(lib):
     assert gemv(ws=None) == -7
     assert gemv(wsb=16) == -7
     assert gemv(dt=9) == -8
+    # the expert-parallel entry points: ranges, counts and peer tables are checked on the host
+    tabs = lambda f, lo, hi, counts: f(p, 8, 16, 4, 8, lo, hi, 256, 128, p, p, p, p, p, counts, 0, None)
+    assert tabs(lib.exl3_moe_decode_tables_range, 0, 4, None) == -1
+    assert tabs(lib.exl3_moe_decode_tables_range, 4, 4, p) == -10
+    assert tabs(lib.exl3_moe_decode_tables_range, 0, 9, p) == -10
+    assert lib.exl3_moe_decode_tables_range(p, 8, 4096, 4, 8, 0, 4, 256, 128, p, p, p, p, p, p, 0, None) == -10
+    ptabs = lambda lo, hi, counts: lib.exl3_moe_prefill_tables_range(p, 8, 512, 4, 8, lo, hi, 256, 128, p, p, p, p, p, p,
+                                                                    counts, 0, None)
+    assert ptabs(0, 4, None) == -1
+    assert ptabs(5, 4, p) == -10
+    blocks = lambda cnt: lib.exl3_gemv_blocks_counted(p, 0, 128, 1, None, None, None, p, 8, 8, 4, 0, p, 1, cnt, 1, None,
+                                                      None, p, 128, 0, p, 1 << 30, 0, None)
+    assert blocks(None) == -1
+    assert blocks(p + 2) == -6
+    u64 = (ctypes.c_uint64 * 2)(p, p)
+    tiles = lambda **kw: lib.exl3_gemm_tiles_peers(p, 0, 128, 256, None, None, None, None, p, 8, 8, 4, 0, p, 1, None,
+                                                   kw.get("y", p), 128, kw.get("map", p), kw.get("yp", u64),
+                                                   kw.get("cp", u64), kw.get("n", 2), kw.get("rpp", 128), p, 1 << 30, 0,
+                                                   None)
+    assert tiles(n=9) == -10
+    assert tiles(map=None) == -1
+    assert tiles(yp=None) == -1
+    assert tiles(rpp=0) == -1
 
 
 def test_layer_container_mirrors_reference_validation():
