@@ -383,6 +383,21 @@ EXL3_API int exl3_moe_prefill_tables_range(const void* indices, int index_bytes,
                                            int32_t* suh_row_dn, int32_t* tiles_gu, int32_t* tiles_dn,
                                            int32_t* counts, unsigned flags, exl3_stream_t stream);
 
+/* ---- trellis encoder (the converter's side of the format) -----------------------------------
+ * Exact Viterbi search of 16x16 tiles over the bitshift trellis with tail-biting closure:
+ * quantize_tile_reference, ponyexl3/convert/reference_search.py:30-87 (float64 path costs, first
+ * minimum wins: the chosen states are bit-identical to the reference's).
+ * w: (n_tiles, 256) float32 in codeword order (ponyexl3/convert/direct.py:409-420 maps a weight
+ * matrix to it); states: (n_tiles, 256) the 16-bit window of every codeword; packed (may be
+ * NULL): (n_tiles, 16K) the packed tiles as stored on disk (pack_trellis_tile,
+ * ponyexl3/ref/trellis.py:12-50).  max_pins: pinned passes after the free one (the reference's
+ * default is 4).  The workspace holds float64 costs and back-pointers of the tiles in flight,
+ * 17 MiB each: exl3_encode_workspace_bytes(n_tiles) is enough for one tile per SM; a smaller
+ * workspace (at least one slot) only lowers the number of tiles in flight. */
+EXL3_API size_t exl3_encode_workspace_bytes(int64_t n_tiles);
+EXL3_API int exl3_encode_tiles(const float* w, int64_t n_tiles, int k, int cb, int max_pins, uint16_t* states,
+                               uint16_t* packed, void* workspace, size_t workspace_bytes, exl3_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

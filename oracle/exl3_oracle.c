@@ -370,6 +370,72 @@ EXL3O_API int exl3o_forward(const uint16_t *x, int64_t rows, const uint16_t *tre
     return rc;
 }
 
+/* ------------------------------------------------------ trellis encoder -- */
+
+/* One Viterbi pass over the bitshift trellis.  Follows _forward,
+ * ponyexl3/convert/reference_search.py:30-57: 65,536 states (16-bit windows), a step appends K
+ * bits (s' = ((s << K) | j) & 0xFFFF), so the predecessors of s' are (s' >> K) | (j << (16-K)),
+ * j = 0 .. 2^K - 1; float64 costs, the FIRST minimum wins among predecessors and among final
+ * states (numpy argmin); branch cost (lut[s'] - w[t])^2 with the product and the sum rounded
+ * separately.  back[t][s'] = chosen predecessor.  Returns the best final state. */
+static int viterbi_forward(const float *w, int k, const double *lut, int init_state, double *cost, double *next,
+                           uint16_t *back)
+{
+    const int kk = 1 << k;
+    for (int s = 0; s < 65536; s++) cost[s] = init_state < 0 ? 0.0 : 1e30;
+    if (init_state >= 0) cost[init_state] = 0.0;
+    for (int t = 0; t < 256; t++) {
+        const double wt = (double)w[t];
+        uint16_t *bt = back + (size_t)t * 65536;
+#pragma omp parallel for schedule(static)
+        for (int s = 0; s < 65536; s++) {
+            const uint32_t base = (uint32_t)s >> k;
+            uint32_t best = base;
+            double cb = cost[base];
+            for (int j = 1; j < kk; j++) {
+                const uint32_t p = base | ((uint32_t)j << (16 - k));
+                if (cost[p] < cb) { cb = cost[p]; best = p; }
+            }
+            const double d = lut[s] - wt;
+            const volatile double d2 = d * d;          /* two roundings, as numpy: no fused multiply-add */
+            next[s] = cb + d2;
+            bt[s] = (uint16_t)best;
+        }
+        double *tmp = cost; cost = next; next = tmp;
+    }
+    int fin = 0;
+    for (int s = 1; s < 65536; s++)
+        if (cost[s] < cost[fin]) fin = s;
+    return fin;
+}
+
+/* Exact trellis search of one tile with tail-biting closure.  Follows quantize_tile_reference,
+ * ponyexl3/convert/reference_search.py:60-87: a free pass proposes the closing state (the window
+ * of codeword 255), pinned passes start from it until the path's pre-state of step 0 and its last
+ * state both equal the pin, or max_pins passes are spent.  w: 256 floats in codeword order. */
+EXL3O_API int exl3o_quantize_tile(const float *w256, int k, int cb, int max_pins, uint16_t *states256)
+{
+    if (k < 1 || k > 8 || cb < 0 || cb > 2 || max_pins < 0) return -1;
+    double *lut = (double *)malloc(65536 * sizeof(double));
+    double *c0 = (double *)malloc(65536 * sizeof(double)), *c1 = (double *)malloc(65536 * sizeof(double));
+    uint16_t *back = (uint16_t *)malloc((size_t)256 * 65536 * sizeof(uint16_t));
+    if (!lut || !c0 || !c1 || !back) { free(lut); free(c0); free(c1); free(back); return -2; }
+    for (uint32_t s = 0; s < 65536u; s++) lut[s] = (double)half_bits_to_float(exl3o_decode_codeword(s, cb));
+    int pin = -1, pre0 = 0;
+    for (int pass = 0; pass <= max_pins; pass++) {
+        int s = viterbi_forward(w256, k, lut, pin, c0, c1, back);
+        for (int t = 255; t >= 0; t--) {
+            states256[t] = (uint16_t)s;
+            s = back[(size_t)t * 65536 + s];
+        }
+        pre0 = s;
+        if (pass > 0 && pre0 == pin && states256[255] == pin) break;
+        pin = states256[255];
+    }
+    free(lut); free(c0); free(c1); free(back);
+    return 0;
+}
+
 EXL3O_API int exl3o_num_threads(void)
 {
 #ifdef _OPENMP

@@ -54,6 +54,7 @@ def lib() -> ctypes.CDLL:
         L.exl3o_forward.argtypes = [p, i64, p, i64, i64, i32, i32, p, p, p, p]
         L.exl3o_half_to_float.argtypes = [p, p, i64]
         L.exl3o_double_to_half.argtypes = [p, p, i64]
+        L.exl3o_quantize_tile.argtypes = [p, i32, i32, i32, p]
         L.exl3o_num_threads.restype = i32
         L.exl3o_set_threads.argtypes = [i32]
         _lib = L
@@ -138,6 +139,18 @@ def unpack_trellis(packed: np.ndarray, k: int) -> np.ndarray:
     out = np.empty(packed.shape[:2] + (256,), dtype=np.uint16)
     lib().exl3o_unpack(_ptr(packed), packed.shape[0] * packed.shape[1], k, _ptr(out))
     return out
+
+
+def quantize_tile(w: np.ndarray, k: int, cb: int = 0, max_pins: int = 4) -> tuple[np.ndarray, np.ndarray]:
+    """ponyexl3/convert/reference_search.py:60-87 (quantize_tile_reference): exact Viterbi search of
+    one tile.  w (256,) float32 in codeword order -> (states (256,) uint16, decoded (256,) float32)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    if w.shape != (256,):
+        raise ValueError(f"expected w shape (256,), got {w.shape}")
+    states = np.empty(256, dtype=np.uint16)
+    if lib().exl3o_quantize_tile(_ptr(w), int(k), int(cb), int(max_pins), _ptr(states)) != 0:
+        raise ValueError("bad K, codebook or max_pins")
+    return states, codebook_table(cb)[states].astype(np.float32)
 
 
 def tensor_core_perm() -> np.ndarray:

@@ -91,6 +91,9 @@ _PROTOTYPES = {
     "exl3_moe_prefill_tables_range": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_uint, c_void_p]),
+    "exl3_encode_workspace_bytes": (c_size_t, [c_int64]),
+    "exl3_encode_tiles": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t,
+                                  c_void_p]),
     "exl3_moe_decode_tables_range": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_uint, c_void_p]),

@@ -120,6 +120,58 @@ def unpack_trellis(packed: torch.Tensor, k: int) -> torch.Tensor:
     return out
 
 
+def quantize_tiles(w: torch.Tensor, k: int, cb: int = 0, max_pins: int = 4,
+                   max_tiles_in_flight: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Exact trellis search of 16x16 tiles (quantize_tile_reference,
+    ponyexl3/convert/reference_search.py:60-87): w (n, 256) float32 in codeword order ->
+    (states (n, 256) int16 holding the 16-bit window of every codeword, packed (n, 16K) int16 tiles
+    as stored on disk).  Bit-identical to the reference's search.  The converter's side of the
+    format: a tile costs 256 steps over 65,536 states, so this is for converting, not for serving."""
+    _need_cuda(w, "w")
+    if w.ndim != 2 or w.shape[1] != 256:
+        raise ValueError(f"expected w of shape (n_tiles, 256), got {tuple(w.shape)}")
+    if not 1 <= k <= 8:
+        raise ValueError(f"K must be in [1, 8], got {k}")
+    w = w.to(torch.float32).contiguous()
+    n = w.shape[0]
+    states = torch.empty((n, 256), dtype=torch.int16, device=w.device)
+    packed = torch.empty((n, 16 * k), dtype=torch.int16, device=w.device)
+    if n == 0:
+        return states, packed
+    lib = _lib.load()
+    with torch.cuda.device(w.device):
+        in_flight = n if max_tiles_in_flight is None else max(1, min(n, max_tiles_in_flight))
+        nbytes = int(lib.exl3_encode_workspace_bytes(in_flight))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+    _lib.check(lib.exl3_encode_tiles(w.data_ptr(), n, k, int(cb), max_pins, states.data_ptr(), packed.data_ptr(),
+                                     ws.data_ptr(), nbytes, _stream(w.device)), "exl3_encode_tiles")
+    return states, packed
+
+
+def tile_codeword_order(device=None) -> torch.Tensor:
+    """perm (256,) int64: codeword i of a tile sits at tile position perm[i] = row * 16 + col
+    (ponyexl3/ref/perm.py:8-26)."""
+    i = torch.arange(256, device=device)
+    t, j = i >> 3, i & 7
+    row = (t & 3) * 2 + (j & 1) + ((j & 2) != 0) * 8
+    col = (t >> 2) + ((j & 4) != 0) * 8
+    return row * 16 + col
+
+
+def quantize_inner(inner: torch.Tensor, k: int, cb: int = 0, max_pins: int = 4) -> torch.Tensor:
+    """Inner weight matrix (in, out) -> packed trellis (in/16, out/16, 16K) int16: tiles in codeword
+    order (ponyexl3/convert/direct.py:409-420), searched by quantize_tiles.  The rotations and
+    scales around the inner matrix are the converter's business."""
+    _need_cuda(inner, "inner")
+    if inner.ndim != 2 or inner.shape[0] % 16 or inner.shape[1] % 16:
+        raise ValueError(f"expected a 2-D matrix with dims that are multiples of 16, got {tuple(inner.shape)}")
+    ti, to = inner.shape[0] // 16, inner.shape[1] // 16
+    tiles = inner.to(torch.float32).reshape(ti, 16, to, 16).permute(0, 2, 1, 3).reshape(ti * to, 256)
+    tiles = tiles[:, tile_codeword_order(inner.device)]
+    _, packed = quantize_tiles(tiles, k, cb, max_pins)
+    return packed.view(ti, to, 16 * k)
+
+
 def decode_packed_trellis(trellis: torch.Tensor, k: int, cb: int, *, n_offset: int = 0,
                           n_count: int | None = None) -> torch.Tensor:
     """Inner weight matrix (in, n_count) fp16 of a packed trellis, bit-exact with the

@@ -157,10 +157,36 @@ def main(ref_root: str) -> None:
     fw["packed_signs_y"] = linear_forward_reconstruct(layer, x).view(np.uint16)
     fw["n_cases"] = np.array([len(names)])
     np.savez_compressed(HERE / "forward.npz", **fw)
+    encoder(ref_root)
     print(f"all done {time.time() - t0:.1f}s")
 
 
+def encoder(ref_root: str) -> None:
+    """Trellis search of single tiles by the reference's exact Viterbi
+    (ponyexl3/convert/reference_search.py); seeds and K follow tests/test_convert.py, plus more
+    K, the other two codebooks and tiles whose first free pass does not close."""
+    sys.path.insert(0, ref_root)
+    from ponyexl3.convert.reference_search import quantize_tile_reference
+    from ponyexl3.ref.codebook import CodebookMode
+
+    t0 = time.time()
+    modes = {0: CodebookMode.DEFAULT, 1: CodebookMode.MCG, 2: CodebookMode.MUL1}
+    cases = [(2, 0, 7, 1.0), (3, 0, 7, 1.0), (4, 0, 11, 1.0), (3, 1, 12, 1.0), (4, 2, 13, 1.0), (1, 0, 14, 1.0),
+             (2, 0, 15, 3.0), (5, 0, 16, 0.7)]
+    enc = {"n_cases": np.array([len(cases)])}
+    for i, (k, cb, seed, scale) in enumerate(cases):
+        w = (np.random.default_rng(seed).standard_normal(256) * scale).astype(np.float32)
+        states, decoded = quantize_tile_reference(w, k=k, cb=modes[cb])
+        enc[f"c{i}_k"], enc[f"c{i}_cb"] = np.array([k]), np.array([cb])
+        enc[f"c{i}_w"], enc[f"c{i}_states"], enc[f"c{i}_decoded"] = w, states.astype(np.uint16), decoded
+        print(f"encoder case {i}: k={k} cb={cb} mse={float(((decoded - w) ** 2).mean()):.5f} {time.time() - t0:.1f}s")
+    np.savez_compressed(HERE / "encoder.npz", **enc)
+
+
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: make_golden.py <path of a checkout of the reference project>")
-    main(sys.argv[1])
+    if len(sys.argv) == 3 and sys.argv[2] == "encoder":      # only the (slow) trellis-search cases
+        encoder(sys.argv[1])
+    elif len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path of a checkout of the reference project> [encoder]")
+    else:
+        main(sys.argv[1])
