@@ -17,6 +17,7 @@ _LAZY = {
     "EXL3MLPMonolith": ".mlp",
     "EXL3SwitchGLU": ".moe",
     "EXL3MoEBlock": ".moe",
+    "EXL3Gemma4MoEBlock": ".moe",
     "EXL3Checkpoint": ".loader",
     "load_exl3_layer": ".loader",
     "list_exl3_layers": ".loader",

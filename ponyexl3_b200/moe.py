@@ -218,22 +218,75 @@ def route_topk(logits: torch.Tensor, top_k: int, norm_topk_prob: bool = True):
 
 
 class EXL3MoEBlock(torch.nn.Module):
-    """Router + stacked experts + weighted sum (ponyexl3/mlx/exl3_moe.py:790-839, without the
-    shared-expert slot, which is one more expert index for the switch)."""
+    """Router + stacked experts + weighted sum (ponyexl3/mlx/exl3_moe.py:790-839).
 
-    def __init__(self, gate_weight: torch.Tensor, switch: EXL3SwitchGLU, top_k: int,
-                 norm_topk_prob: bool = True):
+    With `shared_gate_weight` the shared expert is stacked as the LAST expert of the switch and
+    its gate value sigmoid(x @ shared_gate_weight.T) is one more routing weight: every token gets
+    the slot (num_experts - 1) appended to its top-k (the reference's Qwen3-Next block, :790-798,
+    :823-829)."""
+
+    def __init__(self, gate_weight: torch.Tensor, switch, top_k: int, norm_topk_prob: bool = True,
+                 shared_gate_weight: torch.Tensor | None = None):
         super().__init__()
-        self.gate_weight = gate_weight          # (E, D) router, unquantised
+        self.gate_weight = gate_weight          # (E or E - 1, D) router, unquantised
+        self.shared_gate_weight = shared_gate_weight    # (1, D) or None
         self.switch_mlp = switch
         self.top_k = top_k
         self.norm_topk_prob = norm_topk_prob
+
+    def route(self, x3: torch.Tensor):
+        """(indices (1, T, k or k + 1), scores): the routing decision alone."""
+        inds, scores = route_topk(x3.float() @ self.gate_weight.float().t(), self.top_k, self.norm_topk_prob)
+        if self.shared_gate_weight is not None:
+            shared_idx = self.switch_mlp.num_experts - 1
+            shared_w = torch.sigmoid(x3.float() @ self.shared_gate_weight.float().t())
+            inds = torch.cat([inds, torch.full_like(inds[..., :1], shared_idx)], dim=-1)
+            scores = torch.cat([scores.to(x3.dtype).float(), shared_w], dim=-1)
+        return inds, scores
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x3 = x.reshape(1, -1, x.shape[-1])
-        inds, scores = route_topk(x3.float() @ self.gate_weight.float().t(), self.top_k,
-                                  self.norm_topk_prob)
+        inds, scores = self.route(x3)
         y = self.switch_mlp(x3, inds)
         return (y.float() * scores[..., None]).sum(dim=-2).to(torch.float16).reshape(lead + (x.shape[-1],))
+
+
+class EXL3Gemma4MoEBlock(torch.nn.Module):
+    """Gemma4's router in front of the stacked experts (ponyexl3/mlx/exl3_moe.py:842-923): RMS norm
+    of the hidden state with weight scale * hidden_size**-0.5, a linear projection to expert
+    scores, top-k of the RAW scores, softmax over the selected k, times a per-expert scale.
+    Called with x alone it returns (indices, weights) as the reference's router slot does; called
+    with the routing it runs the experts and the weighted sum."""
+
+    def __init__(self, proj_weight: torch.Tensor, scale: torch.Tensor, per_expert_scale: torch.Tensor, switch,
+                 top_k: int, eps: float, hidden_size: int):
+        super().__init__()
+        self.proj_weight = proj_weight          # (E, D)
+        self.scale = scale                      # (D,)
+        self.per_expert_scale = per_expert_scale  # (E,)
+        self.switch_mlp = switch
+        self.top_k = top_k
+        self.eps = eps
+        self._root_scale = hidden_size ** -0.5
+
+    def route(self, h: torch.Tensor):
+        h32 = h.float()
+        normed = h32 * torch.rsqrt(h32.pow(2).mean(dim=-1, keepdim=True) + self.eps) * (self.scale.float() * self._root_scale)
+        expert_scores = normed @ self.proj_weight.float().t()
+        weights, inds = torch.topk(expert_scores, self.top_k, dim=-1)
+        weights = torch.softmax(weights, dim=-1) * self.per_expert_scale.float()[inds]
+        return inds, weights
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, top_k_indices: torch.Tensor | None = None,
+                top_k_weights: torch.Tensor | None = None):
+        if top_k_indices is None:
+            return self.route(x)
+        lead = x.shape[:-1]
+        x3 = x.reshape(1, -1, x.shape[-1])
+        kk = top_k_indices.shape[-1]
+        y = self.switch_mlp(x3, top_k_indices.reshape(1, -1, kk))
+        w = top_k_weights.reshape(1, -1, kk).float()
+        return (w[..., None] * y.float()).sum(dim=-2).to(torch.float16).reshape(lead + (x.shape[-1],))
