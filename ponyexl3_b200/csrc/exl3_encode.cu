@@ -12,8 +12,9 @@
 // codeword 255's): a free pass proposes the closing state, pinned passes start from it until
 // the path's pre-state of step 0 and its last state both equal the pin (at most max_pins passes).
 //
-// One CTA of 1024 threads per tile: thread i owns states i + 1024 m.  The two cost arrays
-// (2 x 512 KiB of float64) and the back-pointers (one byte per state and step: 16 MiB) live in
+// One CTA of 1024 threads per tile: a thread owns the bases (s' >> K) i + 1024 m and writes the
+// 2^K successor states of each.  The two cost arrays
+// (2 x 512 KiB of float64) and the back-pointers (one byte per base and step, in a 16 MiB area) live in
 // a workspace slot of the CTA and stay in L2; the cost arrays are read and written with
 // cache-global accesses because every step reads what other threads of the CTA wrote in the
 // step before.  The only synchronisation is the CTA barrier: nothing waits on another CTA.
@@ -69,17 +70,23 @@ __global__ void __launch_bounds__(1024) encode_kernel(const EncodeArgs a)
             for (int t = 0; t < 256; t++) {
                 const double wt = (double)sh_w[t];
                 uint8_t* bt = back + (size_t)t * kEncStates;
-                for (int s = tid; s < kEncStates; s += 1024) {
-                    const uint32_t base = (uint32_t)s >> k;
+                // The 2^K successors of one base (s' >> K) share their predecessor set, hence its
+                // cheapest member: every cost of the step before is read exactly once.
+                for (uint32_t base = tid; base < (uint32_t)(kEncStates >> k); base += 1024) {
                     double cb = __ldcg(cur + base);
                     int best = 0;
                     for (int j = 1; j < kk; j++) {
                         const double c = __ldcg(cur + (base | ((uint32_t)j << (16 - k))));
                         if (c < cb) { cb = c; best = j; }
                     }
-                    const double d = (double)__half2float(decode_one<CB>((uint32_t)s)) - wt;
-                    __stcg(nxt + s, __dadd_rn(cb, __dmul_rn(d, d)));
-                    __stcg(bt + s, (uint8_t)best);
+                    __stcg(bt + base, (uint8_t)best);          // one back-pointer for all 2^K successors
+                    for (int low = 0; low < kk; low += 2) {
+                        const uint32_t s = (base << k) | (uint32_t)low;
+                        const double d0 = (double)__half2float(decode_one<CB>(s)) - wt;
+                        const double d1 = (double)__half2float(decode_one<CB>(s + 1)) - wt;
+                        __stcg(reinterpret_cast<double2*>(nxt + s),
+                               make_double2(__dadd_rn(cb, __dmul_rn(d0, d0)), __dadd_rn(cb, __dmul_rn(d1, d1))));
+                    }
                 }
                 __syncthreads();
                 double* tmp = cur; cur = nxt; nxt = tmp;
@@ -116,7 +123,7 @@ __global__ void __launch_bounds__(1024) encode_kernel(const EncodeArgs a)
                 uint32_t s = (uint32_t)sh_fin;
                 for (int t = 255; t >= 0; t--) {
                     sh_states[t] = (uint16_t)s;
-                    const uint32_t j = __ldcg(back + (size_t)t * kEncStates + s);
+                    const uint32_t j = __ldcg(back + (size_t)t * kEncStates + (s >> k));
                     s = (s >> k) | (j << (16 - k));
                 }
                 const int last = sh_states[255];
