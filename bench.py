@@ -808,7 +808,7 @@ def run_gemm(args):
                      "frac": flops / (ms * 1e-3) / 1e12 / 1657.8, "traffic": None,
                      "peak_kind": "of measured (burst bf16 GEMM); sustained 1408.3",
                      "frac_of_sustained": flops / (ms * 1e-3) / 1e12 / 1408.3,
-                     "kernel": "exl3::gemm_kernel (tcgen05) + exl3::hadamard_kernel",
+                     "kernel": "exl3::gemm_kernel (tcgen05) + exl3::hadamard_mma_kernel",
                      "rotation_ms": rot_ms, "gemm_kernel_ms_est": ms - rot_ms,
                      "gemm_kernel_tflops_est": flops / ((ms - rot_ms) * 1e-3) / 1e12,
                      "note": "achieved = FLOPs of the call / time of the call (rotation kernel included); the "
@@ -822,11 +822,96 @@ def run_gemm(args):
     emit(line)
 
 
+def run_encode(args):
+    """The converter's tile search: exact Viterbi encoding of 16x16 tiles of N(0,1) weights at K = 4,
+    3INST (one whole wave of tiles per SM and then some).  A step = one exl3_encode_tiles call over
+    592 tiles; value = tiles per second.  The search lives in L2 (costs and back-pointers of the
+    tiles in flight), so the roofline line reports its algorithmic traffic against the HBM peak only
+    for scale; the CPU baseline is the C oracle's search on all host cores."""
+    import numpy as np
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback for the product path)")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    from ponyexl3_b200 import ops
+
+    n, k, cb = 592, 4, 0
+    g = torch.Generator(device=dev).manual_seed(5000)
+    w = torch.randn((n, 256), device=dev, generator=g)
+    for _ in range(max(args.warmup, 3)):
+        ops.quantize_tiles(w, k, cb)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = max(1, min(args.steps, 20))
+    e0.record()
+    for _ in range(steps):
+        states, packed = ops.quantize_tiles(w, k, cb)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    clocks = sampler.stop()
+    # end to end: weights from pinned host memory, packed tiles back
+    h_w = w.cpu().pin_memory()
+    h_p = torch.empty((n, 16 * k), dtype=torch.int16).pin_memory()
+    d_w = torch.empty_like(w)
+    t0 = time.perf_counter()
+    for _ in range(3):
+        d_w.copy_(h_w, non_blocking=True)
+        h_p.copy_(ops.quantize_tiles(d_w, k, cb)[1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_s = (time.perf_counter() - t0) / 3
+    cpu = None
+    if not args.no_cpu:
+        from oracle import exl3_oracle as oracle
+        oracle.lib()
+        cores = oracle.host_cores()
+        oracle.set_threads(cores)
+        wn = w.cpu().numpy()
+        t0 = time.perf_counter()
+        m = 0
+        while time.perf_counter() - t0 < 10.0 and m < n:
+            st, _ = oracle.quantize_tile(wn[m], k, cb)
+            assert (st == states[m].cpu().numpy().view(np.uint16)).all(), "encoder differs from the oracle"
+            m += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": m / dt, "unit": "tiles/s", "cores": cores, "kind": "port",
+               "sample": f"the first {m} of the {n} tiles through the C oracle's search (each checked against the GPU's "
+                         f"states), {dt:.1f} s"}
+    # per pass and step: 65,536 float64 costs read and written, 4,096 back-pointer bytes
+    step_bytes = 2 * 65536 * 8 + (65536 >> k)
+    emit({
+        "metric": "exl3_trellis_encode_tiles_per_s", "value": n / (ms * 1e-3), "unit": "tiles/s", "n_gpus": 1,
+        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": f"trellis encoder: exact Viterbi search of {n} tiles (16x16, N(0,1)), K={k}, 3INST, "
+                               "up to 4 pinned passes", "tiles": n, "k": k, "codebook": "3INST",
+                   "l2": "the costs and back-pointers of the 148 tiles in flight (2.6 GB) exceed the 126 MB L2 as a "
+                         "whole; a tile's two cost arrays (1 MiB) stay in it"},
+        "roofline": {"bound": "hbm", "achieved": n * 256 * step_bytes / (ms * 1e-3) / 1e9, "peak": 6551.4,
+                     "unit": "GB/s", "frac": n * 256 * step_bytes / (ms * 1e-3) / 1e9 / 6551.4, "traffic": None,
+                     "peak_kind": "of measured (for scale: the search is bound by L2 latency and one CTA barrier "
+                                  "per step, not by DRAM)",
+                     "kernel": "exl3::encode_kernel",
+                     "note": "achieved counts ONE pass per tile (costs read and written, back-pointers written, "
+                             "per step); tiles take 1-5 passes"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": n / e2e_s, "unit": "tiles/s", "h2d_bytes_per_step": n * 256 * 4,
+                "d2h_bytes_per_step": n * 16 * k * 2, "ms_per_step": 1e3 * e2e_s,
+                "api": "ops.quantize_tiles, pinned host weights in, packed tiles out"},
+        "gpu_launches": steps, "clocks": clocks, "kernel_status": 0,
+    })
+
+
 def run_moe(args):
     """The MoE expert-layer configuration: stacked-expert SwitchGLU, 256 experts, top-8, hidden 2048, expert
     intermediate 512, K=4, router logits N(0,1) -> softmax top-8, for --tokens 1, 16 or 4096.
     N > 1: experts partitioned by expert; few tokens are replicated and the partial outputs summed
-    (all-reduce), many tokens are partitioned and their rows exchanged with two all-to-alls.
+    (all-reduce), many tokens are partitioned, gathered, and every output row is stored into the memory
+    of the rank that owns its token.
     A step = one SwitchGLU forward (expert outputs before the router-weighted sum)."""
     import torch
 
@@ -1137,10 +1222,10 @@ def main():
     ap.add_argument("--sweep-cb", default="0,1,2")
     ap.add_argument("--sweep-iters", type=int, default=5)
     ap.add_argument("--sweep-out", default=None, help="write a markdown table of the sweep here")
-    ap.add_argument("--workload", choices=["gemv", "single", "gemm", "decode", "moe"], default="gemv",
+    ap.add_argument("--workload", choices=["gemv", "single", "gemm", "decode", "moe", "encode"], default="gemv",
                     help="gemv = the headline batch-1 GEMV ring; single = one 4096x4096 layer (ring of copies); "
                          "gemm = the 8192-token prefill GEMM; decode = the 64-layer decode step; "
-                         "moe = the 256-expert SwitchGLU layer")
+                         "moe = the 256-expert SwitchGLU layer; encode = the converter's exact tile search")
     ap.add_argument("--gemm-rows", type=int, default=8192, help="gemm workload: tokens per call")
     ap.add_argument("--tokens", type=int, default=1, help="moe workload: tokens per step (1, 16, 4096)")
     ap.add_argument("--rows", type=int, default=1, help="decode workload: new positions per step (1 or 16)")
@@ -1167,6 +1252,8 @@ def main():
         run_gemm(args)
     elif args.workload == "decode":
         run_decode(args)
+    elif args.workload == "encode":
+        run_encode(args)
     elif args.workload == "moe":
         run_moe(args)
     else:
