@@ -427,7 +427,8 @@ int launch_hadamard(const void* x, int x_dtype, int64_t rows, int64_t n, int64_t
     if (rows * (n >> 7) >= ((int64_t)1 << 31)) return EXL3_E_RANGE;   // the kernel counts blocks in 32 bits
     // Many rows into a plain fp16 matrix (the prefill GEMM's operand): 16-row blocks on the tensor cores.
     // (a GLU over bf16 / fp32 rows stays on the butterfly kernel, which applies it before the fp16 rounding)
-    const bool mma = out_mode == HAD_OUT_F16 && !post && !post_row && rows >= kHadamardMmaMinRows &&
+    // (a row count read from the device always takes this kernel, however few rows there may be)
+    const bool mma = out_mode == HAD_OUT_F16 && !post && !post_row && (rows >= kHadamardMmaMinRows || rows_dev) &&
                      (!glu || x_dtype == EXL3_DT_F16) &&
                      x_row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                      (!pre || (reinterpret_cast<uintptr_t>(pre) & 15) == 0) && (reinterpret_cast<uintptr_t>(out) & 15) == 0;

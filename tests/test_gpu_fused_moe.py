@@ -237,9 +237,9 @@ def test_decode_over_an_expert_range_sums_to_the_full_switch(cuda, oracle, world
     assert rel_err(total.cpu().numpy(), want) <= 2e-3
 
 
-@pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("act", ["silu", "gelu"])
-def test_prefill_over_an_expert_range_stores_rows_at_their_owners(cuda, oracle, world, act):
+@pytest.mark.parametrize("world,act,T,kk", [(2, "silu", 96, 4), (4, "silu", 96, 4), (2, "gelu", 96, 4), (4, "gelu", 96, 4),
+                                            (2, "silu", 20, 2)])
+def test_prefill_over_an_expert_range_stores_rows_at_their_owners(cuda, oracle, world, act, T, kk):
     """Expert parallelism for many tokens, every rank's share computed one after the other on
     this GPU: tokens are partitioned (buffer p holds the output rows of partition p), a rank
     sorts and tiles only the pairs of its experts (their number stays on the device), its down
@@ -251,7 +251,7 @@ def test_prefill_over_an_expert_range_stores_rows_at_their_owners(cuda, oracle, 
     from ponyexl3_b200 import ops
     from ponyexl3_b200.parallel import shard_expert_weights, shard_experts
 
-    E, D, H, kk, k, T = 16, 256, 128, 4, 4, 96
+    E, D, H, k = 16, 256, 128, 4            # the last case: fewer than 64 pairs in all
     w = _experts(E, D, H, k, seed=930 + world)
     rng = np.random.default_rng(31 + world)
     x = (rng.standard_normal((T, D)) * 0.5).astype(np.float16)
